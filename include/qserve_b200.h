@@ -202,6 +202,48 @@ QS_API int qs_single_query_attention_quant(const void* q, const void* k, const v
 QS_API int qs_argmax_rows(int64_t* out, const void* logits, int rows, int vocab, void* stream);
 QS_API int qs_silu_and_mul_quant(int8_t* out, const void* input, void* input_sum, void* scale, int tokens, int d, void* stream);
 
+/* ---------------------------------------------------------------------------------------------------------
+ * Unquantised hybrid decoders (qserve_b200/hybrid.py): attention layers and recurrent layers in one stack over an fp32
+ * residual stream.  Not part of the reference surface.  `dtype` is the storage type of activations, weights tables and
+ * the key/value cache; norms, scores, softmax weights, rotary angles, decays, the recurrent state and the stream are fp32.
+ * All kernels take a FLAT batch of tokens with per-token tables (slot of the sequence, position) and, for the recurrent
+ * layer, per-entry tables (first row, length, slot, position of the first token of each sequence's run of tokens).
+ * --------------------------------------------------------------------------------------------------------- */
+#define QS_DTYPE_BF16 0
+#define QS_DTYPE_F32 1
+/* out[t] = table[tokens[t]] + pair_table[prev[t] < 0 ? buckets : (prev[t] * mul_prev + tokens[t] * mul_cur) % buckets]; pair_table may be NULL */
+QS_API int qs_hyb_embed(float* out, const int32_t* tokens, const int32_t* prev, const void* table, const void* pair_table, int tokens_n,
+                        int width, int buckets, int64_t mul_prev, int64_t mul_cur, int dtype, void* stream);
+/* out_k = x * rsqrt(mean(x^2) + eps) * (offset + w_k), k = 1, 2 (out2 / w2 may be NULL); x fp32 [tokens, width], w fp32 */
+QS_API int qs_hyb_rms_norm(void* out1, void* out2, const float* x, const float* w1, const float* w2, float offset, float eps, int tokens_n,
+                           int width, int dtype, void* stream);
+/* x[i] += y[i] (x fp32, y in the storage type) */
+QS_API int qs_hyb_residual_add(float* x, const void* y, int64_t n, int dtype, void* stream);
+/* out[t, i] = gelu_tanh(in[t, i]) * in[t, ff + i]; out rows of out_stride elements */
+QS_API int qs_hyb_gelu_tanh_mul(void* out, int64_t out_stride, const void* in, int tokens_n, int ff, int dtype, void* stream);
+/* interleaved rotary embedding (angle = position * inv_freq[pair], cos / sin times `amplitude`) of the first rot_dims entries of every
+ * query / key map of the projection rows [H*maps*dim q | G*maps*dim k | G*vdim v] (q in place), keys and values appended to the pages
+ * K [page][page_size][G][maps*dim], V [page][page_size][G][vdim] through block_table [slots, max_blocks] */
+QS_API int qs_hyb_rope_append(void* proj, int64_t stride, const int32_t* tok_slot, const int32_t* tok_pos, const int32_t* block_table,
+                              int max_blocks, void* kpool, void* vpool, const float* inv_freq, float amplitude, int tokens_n, int heads,
+                              int kv_heads, int maps, int dim, int vdim, int rot_dims, int page_size, int dtype, void* stream);
+/* causal attention of every token over positions 0..tok_pos of its sequence in the paged cache, `maps` (1 or 2) softmax maps per head
+ * over shared values: o = a1 [- lambda a2]; head_norm: o *= rsqrt(mean(o^2) + eps); o *= out_scale.  out [tokens, heads*vdim] */
+QS_API int qs_hyb_attention(void* out, int64_t out_stride, const void* q, int64_t q_stride, const void* kpool, const void* vpool,
+                            const int32_t* tok_slot, const int32_t* tok_pos, const int32_t* block_table, int max_blocks, int tokens_n,
+                            int heads, int kv_heads, int maps, int dim, int vdim, float scale, float lambda, float out_scale, float eps,
+                            int head_norm, int page_size, int dtype, void* stream);
+/* gated delta rule over projection rows [G*dim q | G*dim k | H*vdim v | H*vdim gate | H b | H a]: short convolution (taps) + silu on
+ * q | k | v, unit q (times dim^-1/2) and k, beta = sigmoid(b), decay = exp(-exp(a_log) softplus(a + dt_bias)), then per head
+ * S <- decay S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q; out = o * rsqrt(mean(o^2) + eps) * norm_w * silu(gate).
+ * state fp32 [slots, H, dim, vdim], conv_state fp32 [slots, taps-1, 2 G dim + H vdim]; a run that starts at position 0 starts from zero.
+ * prep fp32 [tokens, 2 G dim + H vdim + 2 H] and o_raw fp32 [tokens, H vdim] are scratch. */
+QS_API int qs_hyb_gated_delta(void* out, int64_t out_stride, float* prep, float* o_raw, const void* proj, int64_t stride, const float* conv_w,
+                              float* conv_state, float* state, const float* a_log, const float* dt_bias, const float* norm_w,
+                              const int32_t* tok_entry, const int32_t* tok_pos, const int32_t* entry_start, const int32_t* entry_len,
+                              const int32_t* entry_slot, const int32_t* entry_pos0, int tokens_n, int entries, int heads, int kv_heads,
+                              int dim, int vdim, int taps, float unit_eps, float eps, int dtype, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -241,3 +241,39 @@ def load_into_runner(runner, fused: Dict[str, torch.Tensor]) -> int:
         if key in fused and (take_norms or "norm" not in key):
             put(t, fused[key], key)
     return n
+
+
+# ------------------------------------------------------------------------------------------------------------------------
+# safetensors: 8-byte little-endian header length, a JSON header (name -> dtype, shape, data_offsets), then the raw data
+# ------------------------------------------------------------------------------------------------------------------------
+_ST_DTYPES = {"BF16": torch.bfloat16, "F16": torch.float16, "F32": torch.float32, "F64": torch.float64, "I64": torch.int64, "I32": torch.int32,
+              "I16": torch.int16, "I8": torch.int8, "U8": torch.uint8, "BOOL": torch.bool}
+
+
+def read_safetensors(path: str) -> Dict[str, torch.Tensor]:
+    """All tensors of a .safetensors file as CPU tensors in their stored dtype (no third-party reader)."""
+    import json
+    import struct
+
+    with open(path, "rb") as f:
+        raw = f.read()
+    (n,) = struct.unpack("<Q", raw[:8])
+    header = json.loads(raw[8:8 + n].decode("utf-8"))
+    data = memoryview(raw)[8 + n:]
+    out: Dict[str, torch.Tensor] = {}
+    for name, m in header.items():
+        if name == "__metadata__":
+            continue
+        dt = _ST_DTYPES.get(m["dtype"])
+        if dt is None:
+            raise ValueError(f"{path}: tensor {name!r} has unsupported dtype {m['dtype']}")
+        lo, hi = m["data_offsets"]
+        shape = tuple(m["shape"])
+        count = 1
+        for s in shape:
+            count *= s
+        if count == 0:
+            out[name] = torch.empty(shape, dtype=dt)
+            continue
+        out[name] = torch.frombuffer(bytearray(data[lo:hi]), dtype=dt, count=count).reshape(shape)
+    return out

@@ -1,0 +1,257 @@
+"""Unquantised hybrid decoders over the library's kernels (csrc/hybrid.cu): a stack of layers, each a sequence mixer (attention over the
+paged cache, or a recurrent layer over a state slot) beside an optional feed-forward, on an fp32 residual stream.
+
+The model is assembled from a `HybridConfig` (qserve_b200.modelcfg): mixers are looked up in `MIXERS` by config type, so another design
+reuses them with other constants.  A forward pass takes a `StepBatch` -- the flat batch a scheduler step has put together (portions of
+prompts beside single decoded tokens) -- and the `HybridCache`; there is no other forward path: whole prompts, portions and decoding
+all go through `HybridDecoder.forward`.
+
+Matrix products are cuBLAS through torch (as the quantised models' lm_head is); everything else is this library's kernels.  With
+`dtype=torch.float32` every product runs in true fp32 (TF32 off).
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+from typing import Dict, List, Optional, Sequence
+
+import torch
+
+from ._lib import check, lib
+from .cache import HybridCache
+from .modelcfg import AttentionMixerConfig, DeltaMixerConfig, HybridConfig
+
+_DT = {torch.bfloat16: 0, torch.float32: 1}
+
+
+def _stream(dev: torch.device):
+    return torch._C._cuda_getCurrentRawStream(dev.index if dev.index is not None else torch.cuda.current_device())
+
+
+def _p(t: Optional[torch.Tensor]):
+    return None if t is None else t.data_ptr()
+
+
+@dataclass
+class StepBatch:
+    """Device-side description of one step's flat token batch.  Row t of every activation belongs to token t."""
+    n_tokens: int
+    n_entries: int
+    tokens: torch.Tensor       # int32 [T]
+    prev: torch.Tensor         # int32 [T] previous token of the same sequence, -1 for a sequence's first token
+    tok_slot: torch.Tensor     # int32 [T] slot (= block-table row) of the token's sequence
+    tok_pos: torch.Tensor      # int32 [T] position in its sequence
+    tok_entry: torch.Tensor    # int32 [T] index of its entry
+    entry_start: torch.Tensor  # int32 [E] first row of the entry
+    entry_len: torch.Tensor    # int32 [E]
+    entry_slot: torch.Tensor   # int32 [E]
+    entry_pos0: torch.Tensor   # int32 [E] position of the entry's first token
+    block_table: torch.Tensor  # int32 [slots, max_blocks]
+
+    @staticmethod
+    def build(entries: Sequence[tuple], block_table: torch.Tensor, device: torch.device) -> "StepBatch":
+        """entries: (slot, first position, previous token or -1, token list) per sequence, in batch order."""
+        T = sum(len(e[3]) for e in entries)
+        E = len(entries)
+        host = torch.empty(5 * T + 4 * E, dtype=torch.int32)
+        tok, prev, slot, pos, ent = (host[i * T:(i + 1) * T] for i in range(5))
+        es, el, eslot, ep0 = (host[5 * T + i * E: 5 * T + (i + 1) * E] for i in range(4))
+        r = 0
+        for i, (s, p0, last, toks) in enumerate(entries):
+            n = len(toks)
+            if n == 0:
+                raise ValueError("an entry of a step must bring at least one token")
+            tt = torch.as_tensor(toks, dtype=torch.int32)
+            tok[r:r + n] = tt
+            prev[r] = last
+            prev[r + 1:r + n] = tt[:-1]
+            slot[r:r + n] = s
+            pos[r:r + n] = torch.arange(p0, p0 + n, dtype=torch.int32)
+            ent[r:r + n] = i
+            es[i], el[i], eslot[i], ep0[i] = r, n, s, p0
+            r += n
+        if device.type == "cuda":
+            host = host.pin_memory()
+        d = host.to(device, non_blocking=True)
+        v = [d[i * T:(i + 1) * T] for i in range(5)] + [d[5 * T + i * E: 5 * T + (i + 1) * E] for i in range(4)]
+        return StepBatch(T, E, *v, block_table)
+
+
+# ------------------------------------------------------------------------------------------------------------------------
+# mixers
+# ------------------------------------------------------------------------------------------------------------------------
+class MultiMapAttentionMixer:
+    """Causal softmax attention over the paged cache with `maps` score maps per head sharing the values; maps = 2 is differential attention:
+    o = a1 - lambda a2 with lambda = exp(lq1 . lk1) - exp(lq2 . lk2) + diff, then unit RMS per head and a factor (1 - diff)."""
+
+    def __init__(self, m: AttentionMixerConfig, w: Dict[str, torch.Tensor], eps: float, dtype, device):
+        self.m, self.eps = m, eps
+        assert m.heads % m.kv_heads == 0
+        self.in_features = (m.heads + m.kv_heads) * m.maps * m.dim + m.kv_heads * m.vdim
+        self.out_features = m.heads * m.vdim
+        for name, rows in (("q", m.heads * m.maps * m.dim), ("k", m.kv_heads * m.maps * m.dim), ("v", m.kv_heads * m.vdim)):
+            if w[name].shape[0] != rows:
+                raise ValueError(f"attention weight {name}: {tuple(w[name].shape)} does not have {rows} rows")
+        self.w_in = torch.cat([w["q"], w["k"], w["v"]], 0).to(device=device, dtype=dtype).contiguous()
+        self.w_out = w["o"]
+        self.inv_freq = torch.tensor(m.rot.inv_freq(), dtype=torch.float64).to(torch.float32).to(device)
+        self.amp = float(m.rot.amplitude())
+        if m.maps == 2:
+            d = lambda a, b: float((w[a].double() * w[b].double()).sum())
+            self.lam = math.exp(d("lq1", "lk1")) - math.exp(d("lq2", "lk2")) + m.diff
+            self.out_scale = 1.0 - m.diff
+        else:
+            self.lam, self.out_scale = 0.0, 1.0
+
+    def scratch_floats(self, tokens: int) -> int:
+        return 0
+
+    def run(self, proj: torch.Tensor, out: torch.Tensor, b: StepBatch, run_cache: dict, page_size: int, scratch, dt: int, stream) -> None:
+        m = self.m
+        check(lib.qs_hyb_rope_append(proj.data_ptr(), proj.stride(0), _p(b.tok_slot), _p(b.tok_pos), _p(b.block_table), b.block_table.shape[1],
+                                     run_cache["k"].data_ptr(), run_cache["v"].data_ptr(), self.inv_freq.data_ptr(), self.amp, b.n_tokens,
+                                     m.heads, m.kv_heads, m.maps, m.dim, m.vdim, m.rot.dims, page_size, dt, stream))
+        check(lib.qs_hyb_attention(out.data_ptr(), out.stride(0), proj.data_ptr(), proj.stride(0), run_cache["k"].data_ptr(),
+                                   run_cache["v"].data_ptr(), _p(b.tok_slot), _p(b.tok_pos), _p(b.block_table), b.block_table.shape[1],
+                                   b.n_tokens, m.heads, m.kv_heads, m.maps, m.dim, m.vdim, m.scale, self.lam, self.out_scale, self.eps,
+                                   1 if m.head_norm else 0, page_size, dt, stream))
+
+
+class GatedDeltaMixer:
+    """Gated delta rule with short convolutions; the state and the convolution's last inputs live in the sequence's slot."""
+
+    def __init__(self, m: DeltaMixerConfig, w: Dict[str, torch.Tensor], eps: float, dtype, device):
+        self.m, self.eps = m, eps
+        assert m.heads % m.kv_heads == 0
+        qk, hv = m.kv_heads * m.dim, m.heads * m.vdim
+        for name, rows in (("q", qk), ("k", qk), ("v", hv), ("g", hv), ("b", m.heads), ("a", m.heads)):
+            if w[name].shape[0] != rows:
+                raise ValueError(f"delta weight {name}: {tuple(w[name].shape)} does not have {rows} rows")
+        self.in_features = 2 * qk + 2 * hv + 2 * m.heads
+        self.out_features = hv
+        self.w_in = torch.cat([w["q"], w["k"], w["v"], w["g"], w["b"], w["a"]], 0).to(device=device, dtype=dtype).contiguous()
+        self.w_out = w["o"]
+        f32 = lambda t: t.to(torch.float32).to(device).contiguous()
+        self.conv_w = f32(torch.cat([w["q.conv"], w["k.conv"], w["v.conv"]], 0))
+        if self.conv_w.shape[1] != m.conv:
+            raise ValueError("convolution weights do not have `conv` taps")
+        self.a_log, self.dt_bias, self.norm_w = f32(w["A_log"]), f32(w["dt_bias"]), f32(w["norm"])
+        self.prep_width = 2 * qk + hv + 2 * m.heads
+
+    def scratch_floats(self, tokens: int) -> int:
+        return tokens * (self.prep_width + self.out_features)
+
+    def run(self, proj: torch.Tensor, out: torch.Tensor, b: StepBatch, run_cache: dict, page_size: int, scratch: torch.Tensor, dt: int, stream) -> None:
+        m, T = self.m, b.n_tokens
+        prep = scratch[: T * self.prep_width]
+        o_raw = scratch[T * self.prep_width: T * (self.prep_width + self.out_features)]
+        check(lib.qs_hyb_gated_delta(out.data_ptr(), out.stride(0), prep.data_ptr(), o_raw.data_ptr(), proj.data_ptr(), proj.stride(0),
+                                     self.conv_w.data_ptr(), run_cache["conv"].data_ptr(), run_cache["state"].data_ptr(), self.a_log.data_ptr(),
+                                     self.dt_bias.data_ptr(), self.norm_w.data_ptr(), _p(b.tok_entry), _p(b.tok_pos), _p(b.entry_start),
+                                     _p(b.entry_len), _p(b.entry_slot), _p(b.entry_pos0), T, b.n_entries, m.heads, m.kv_heads, m.dim, m.vdim,
+                                     m.conv, m.unit_eps, self.eps, dt, stream))
+
+
+MIXERS = {AttentionMixerConfig: MultiMapAttentionMixer, DeltaMixerConfig: GatedDeltaMixer}
+
+
+# ------------------------------------------------------------------------------------------------------------------------
+# the decoder
+# ------------------------------------------------------------------------------------------------------------------------
+class _Layer:
+    def __init__(self, mixer, norm1, norm2, w_mlp_in, w_out, ff):
+        self.mixer, self.norm1, self.norm2, self.w_mlp_in, self.w_out, self.ff = mixer, norm1, norm2, w_mlp_in, w_out, ff
+
+
+class HybridDecoder:
+    """x <- x + (mixer(norm1 x) + ff(norm2 x)) per layer run, both branches of the same x; the two output projections are ONE product:
+    [mixer heads | ff activation] @ [W_o | W_down]^T, so the sum of the branches is accumulated in fp32 inside the GEMM."""
+
+    def __init__(self, cfg: HybridConfig, weights: Dict[str, torch.Tensor], dtype: torch.dtype = torch.bfloat16, device: Optional[torch.device] = None):
+        if dtype not in _DT:
+            raise ValueError("dtype must be torch.bfloat16 or torch.float32")
+        self.cfg, self.dtype, self.dt = cfg, dtype, _DT[dtype]
+        self.device = dev = device or torch.device("cuda", torch.cuda.current_device())
+        if dev.type != "cuda":
+            raise RuntimeError("qserve_b200 has no CPU path: HybridDecoder needs a CUDA device")
+        if dtype == torch.float32:
+            torch.backends.cuda.matmul.allow_tf32 = False
+            torch.backends.cudnn.allow_tf32 = False
+        st = lambda t: t.to(device=dev, dtype=dtype).contiguous()
+        f32 = lambda t: t.to(torch.float32).to(dev).contiguous()
+        W = cfg.width
+        if tuple(weights["embed"].shape) != (cfg.vocab, W) or tuple(weights["head"].shape) != (cfg.vocab, W):
+            raise ValueError("embed / head do not match vocab x width")
+        self.embed = st(weights["embed"])
+        self.pair = st(weights["bigram"]) if cfg.pair_buckets > 0 else None
+        if self.pair is not None and self.pair.shape[0] != cfg.pair_buckets + 1:
+            raise ValueError("the pair table must have buckets + 1 rows")
+        self.head = st(weights["head"])
+        self.final_norm = f32(weights["final.norm"])
+        self.layers: List[_Layer] = []
+        for i, ly in enumerate(cfg.layers):
+            pre = f"l{i}."
+            mw = {k[len(pre) + 4:]: v for k, v in weights.items() if k.startswith(pre + "mix.")}
+            mixer = MIXERS[type(ly.mixer)](ly.mixer, mw, cfg.eps, dtype, dev)
+            outs = [mixer.w_out]
+            w_mlp_in, norm2, ff = None, None, 0
+            if ly.mlp is not None:
+                ff = ly.mlp.ff
+                w_mlp_in = st(torch.cat([weights[pre + "mlp.gate"], weights[pre + "mlp.up"]], 0))
+                outs.append(weights[pre + "mlp.down"])
+                norm2 = f32(weights[pre + "norm2"])
+            w_out = st(torch.cat(outs, 1))  # [W, heads*vdim + ff]
+            del mixer.w_out
+            self.layers.append(_Layer(mixer, f32(weights[pre + "norm1"]), norm2, w_mlp_in, w_out, ff))
+        self.schedule = cfg.schedule()
+        self._scratch: Optional[torch.Tensor] = None
+
+    @classmethod
+    def from_dir(cls, model_dir: str, dtype: torch.dtype = torch.bfloat16, device: Optional[torch.device] = None) -> "HybridDecoder":
+        import os
+
+        from .checkpoint import read_safetensors
+        from .modelcfg import read_model_config
+
+        return cls(read_model_config(model_dir), read_safetensors(os.path.join(model_dir, "model.safetensors")), dtype, device)
+
+    def new_cache(self, max_tokens: int, max_seqs: int = 4, page_size: int = 64) -> HybridCache:
+        return HybridCache(self.cfg, self.dtype, self.device, max_tokens, max_seqs, page_size)
+
+    # ----------------------------------------------------------------------------------------------------------------
+    def forward(self, b: StepBatch, cache: HybridCache, tap=None) -> torch.Tensor:
+        """Residual stream [T, W] fp32 after the last layer run.  `tap(run_index, x)` (debugging / tests) sees it after every run."""
+        cfg, dev, dt, T, W = self.cfg, self.device, self.dt, b.n_tokens, self.cfg.width
+        s = _stream(dev)
+        x = torch.empty((T, W), dtype=torch.float32, device=dev)
+        check(lib.qs_hyb_embed(x.data_ptr(), _p(b.tokens), _p(b.prev), self.embed.data_ptr(), _p(self.pair), T, W, cfg.pair_buckets,
+                               cfg.pair_mul_prev, cfg.pair_mul_cur, dt, s))
+        need = max(ly.mixer.scratch_floats(T) for ly in self.layers)
+        if need and (self._scratch is None or self._scratch.numel() < need):
+            self._scratch = torch.empty(need, dtype=torch.float32, device=dev)
+        h1 = torch.empty((T, W), dtype=self.dtype, device=dev)
+        h2 = torch.empty((T, W), dtype=self.dtype, device=dev)
+        for run, li in enumerate(self.schedule):
+            ly = self.layers[li]
+            check(lib.qs_hyb_rms_norm(h1.data_ptr(), _p(h2) if ly.ff else None, x.data_ptr(), ly.norm1.data_ptr(), _p(ly.norm2), cfg.norm_offset,
+                                      cfg.eps, T, W, dt, s))
+            proj = torch.mm(h1, ly.mixer.w_in.t())
+            cat = torch.empty((T, ly.mixer.out_features + ly.ff), dtype=self.dtype, device=dev)
+            ly.mixer.run(proj, cat, b, cache.runs[run], cache.page_size, self._scratch, dt, s)
+            if ly.ff:
+                gu = torch.mm(h2, ly.w_mlp_in.t())
+                check(lib.qs_hyb_gelu_tanh_mul(cat.data_ptr() + ly.mixer.out_features * cat.element_size(), cat.stride(0), gu.data_ptr(), T, ly.ff, dt, s))
+            upd = torch.mm(cat, ly.w_out.t())
+            check(lib.qs_hyb_residual_add(x.data_ptr(), upd.data_ptr(), T * W, dt, s))
+            if tap is not None:
+                tap(run, x)
+        return x
+
+    def logits(self, x_rows: torch.Tensor) -> torch.Tensor:
+        """Final norm and vocabulary projection of the given stream rows -> fp32 [n, vocab]."""
+        n, W = x_rows.shape
+        x_rows = x_rows.contiguous()
+        h = torch.empty((n, W), dtype=self.dtype, device=self.device)
+        check(lib.qs_hyb_rms_norm(h.data_ptr(), None, x_rows.data_ptr(), self.final_norm.data_ptr(), None, self.cfg.norm_offset, self.cfg.eps, n, W,
+                                  self.dt, _stream(self.device)))
+        return torch.mm(h, self.head.t()).float()

@@ -29,3 +29,147 @@ MODELS = {
 }
 
 PRECISIONS = ("w4a8kv4", "w4a8kv4-g128", "w8a8kv8", "w4a8kv8", "w8a8kv4")
+
+
+# ------------------------------------------------------------------------------------------------------------------------
+# Hybrid decoders described by a config.json: a list of layers, each with a sequence mixer (softmax attention over a paged cache or a
+# recurrent layer with a per-sequence state) and an optional feed-forward.  Pure Python; the engine lives in qserve_b200.hybrid.
+# ------------------------------------------------------------------------------------------------------------------------
+import json
+import math
+import os
+from typing import Callable, Dict, Optional, Tuple
+
+
+@dataclass(frozen=True)
+class RotaryConfig:
+    """Interleaved rotary embedding on the first `dims` entries of a head; optional YaRN blend of the frequencies."""
+    dims: int
+    base: float
+    factor: Optional[float] = None   # None: no scaling
+    original: float = 0.0
+    fast: float = 0.0
+    slow: float = 0.0
+
+    def inv_freq(self):
+        """Per-pair angular frequency (float64 list).  With scaling, pair i is blended between f_i and f_i / factor by a linear ramp whose
+        ends are the pair indices that make `fast` and `slow` turns over the original context length."""
+        half = self.dims // 2
+        f = [self.base ** (-2.0 * i / self.dims) for i in range(half)]
+        if self.factor is None:
+            return f
+        turn = lambda t: self.dims * math.log(self.original / (2.0 * math.pi * t)) / (2.0 * math.log(self.base))
+        lo = max(math.floor(turn(self.fast)), 0)
+        hi = min(math.ceil(turn(self.slow)), self.dims - 1)
+        out = []
+        for i in range(half):
+            ramp = min(max((i - lo) / max(hi - lo, 0.001), 0.0), 1.0)
+            out.append(f[i] / self.factor * ramp + f[i] * (1.0 - ramp))
+        return out
+
+    def amplitude(self) -> float:
+        return 1.0 if self.factor is None else 0.1 * math.log(self.factor) + 1.0
+
+
+@dataclass(frozen=True)
+class AttentionMixerConfig:
+    """Causal softmax attention with `maps` score maps per head over shared values (2 = differential attention)."""
+    heads: int
+    kv_heads: int
+    dim: int
+    vdim: int
+    rot: RotaryConfig
+    scale: float
+    maps: int = 1
+    diff: float = 0.0        # differential attention: offset of lambda, and (1 - diff) scales the normalised head output
+    head_norm: bool = False  # unit-RMS per head after the maps are combined
+
+
+@dataclass(frozen=True)
+class DeltaMixerConfig:
+    """Gated delta rule: per head a [dim, vdim] fp32 state; short causal convolution of `conv` taps on q, k, v."""
+    heads: int
+    kv_heads: int
+    dim: int
+    vdim: int
+    conv: int
+    unit_eps: float = 1e-6
+
+
+@dataclass(frozen=True)
+class MlpConfig:
+    kind: str
+    ff: int
+
+
+@dataclass(frozen=True)
+class HybridLayerConfig:
+    type: str
+    mixer: object
+    mlp: Optional[MlpConfig]
+
+
+@dataclass(frozen=True)
+class HybridConfig:
+    architecture: str
+    vocab: int
+    width: int
+    eps: float
+    layers: Tuple[HybridLayerConfig, ...]
+    loop_start: int = 0
+    loop_stop: int = 0
+    loop_times: int = 1
+    pair_buckets: int = 0    # 0: no (previous, current) pair embedding
+    pair_mul_prev: int = 0
+    pair_mul_cur: int = 0
+    norm_offset: float = 1.0  # gains are stored as offsets from this value
+
+    def schedule(self):
+        """Layer index of every layer RUN: layers loop_start .. loop_stop-1 run loop_times times in a row (same weights, own cache / state)."""
+        n = len(self.layers)
+        return list(range(self.loop_start)) + list(range(self.loop_start, self.loop_stop)) * self.loop_times + list(range(self.loop_stop, n))
+
+
+def _parse_rot(r: dict) -> RotaryConfig:
+    sc = r.get("scaling")
+    if sc:
+        return RotaryConfig(int(r["dims"]), float(r["base"]), float(sc["factor"]), float(sc["original"]), float(sc["fast"]), float(sc["slow"]))
+    return RotaryConfig(int(r["dims"]), float(r["base"]))
+
+
+def parse_rizurax(c: dict) -> HybridConfig:
+    """Rizurax: parallel layers (mixer and feed-forward read the same stream), mixers `attention` (differential, two maps per head, unit-RMS
+    heads) and `delta` (gated delta rule), hashed pair embedding, a looped span of layers."""
+    layers = []
+    for ly in c["layers"]:
+        m = ly["mixer"]
+        if ly["type"] == "attention":
+            mixer = AttentionMixerConfig(int(m["heads"]), int(m["kv_heads"]), int(m["dim"]), int(m["vdim"]), _parse_rot(m["rot"]), float(m["scale"]),
+                                         maps=2, diff=float(m["diff"]), head_norm=True)
+        elif ly["type"] == "delta":
+            mixer = DeltaMixerConfig(int(m["heads"]), int(m["kv_heads"]), int(m["dim"]), int(m["vdim"]), int(m["conv"]))
+        else:
+            raise ValueError(f"unknown mixer type {ly['type']!r}")
+        mlp = ly.get("mlp")
+        if mlp is not None and mlp.get("kind") != "dense":
+            raise ValueError(f"unknown feed-forward kind {mlp.get('kind')!r}")
+        layers.append(HybridLayerConfig(ly["type"], mixer, MlpConfig("dense", int(mlp["ff"])) if mlp is not None else None))
+    lp = c.get("loop") or {}
+    bg = (c.get("embedding") or {}).get("bigram") or {}
+    return HybridConfig("Rizurax", int(c["vocab"]), int(c["width"]), float(c["norm"]["eps"]), tuple(layers),
+                        int(lp.get("start", 0)), int(lp.get("stop", 0)), int(lp.get("times", 1)),
+                        int(bg.get("buckets", 0)), int(bg.get("mul_prev", 0)), int(bg.get("mul_cur", 0)))
+
+
+# config.json "architecture" -> parser.  The quantised Llama-family models of MODELS are built by qserve_b200.decode.DecodeRunner.
+ARCHITECTURES: Dict[str, Callable[[dict], HybridConfig]] = {"Rizurax": parse_rizurax}
+
+
+def read_model_config(model_dir: str) -> HybridConfig:
+    """Parse `<model_dir>/config.json` with the parser its "architecture" names."""
+    with open(os.path.join(model_dir, "config.json")) as f:
+        c = json.load(f)
+    arch = c.get("architecture")
+    if arch not in ARCHITECTURES:
+        raise ValueError(f"unknown architecture {arch!r}; known: {sorted(ARCHITECTURES)}")
+    return ARCHITECTURES[arch](c)
