@@ -55,6 +55,8 @@ def parse():
     ap.add_argument("--no-graph", action="store_true", help="eager launches instead of CUDA-graph replay")
     ap.add_argument("--no-fused", action="store_true", help="use exactly the reference op sequence (no fused add+norm / silu+quant extensions)")
     ap.add_argument("--kernel-reps", type=int, default=5)
+    ap.add_argument("--hybrid", action="store_true", help="instead of the default workload: prefill and decode throughput of the Rizurax hybrid decoder "
+                    "(random weights) at layer sizes of real models, beside the Llama-style W4A8KV4 runner at equal size; prints one JSON line")
     return ap.parse_args()
 
 
@@ -628,6 +630,123 @@ def tp_block(args, rank, world, dev, hbm_gbs):
 
 
 # ------------------------------------------------------------------------------------------------------------
+# --hybrid: the unquantised hybrid decoder (differential attention + gated delta rule) beside the closest existing model
+# ------------------------------------------------------------------------------------------------------------
+HYBRID_SIZES = {  # name: width, heads, kv heads, head size (per map / value), feed-forward, vocab
+    "w2048": (2048, 16, 4, 128, 8192, 32000),
+    "w4096": (4096, 32, 8, 128, 14336, 32000),
+}
+
+
+def hybrid_block(args):
+    """Prefill (4 prompts x 2048 tokens in one step) and decode (64 sequences at 1024 tokens of context) of a four-layer stack attention |
+    delta | attention | delta with a feed-forward in every layer, captured in CUDA graphs (device time of the step, host excluded), and the
+    kernels of the design timed one by one with their algorithmic bytes / flops against the measured copy and bf16 GEMM peaks.  Beside it,
+    at equal width / heads / feed-forward: the Llama-style W4A8KV4 decode step and the kernels that play the same parts there."""
+    import torch
+
+    from qserve_b200 import backend
+    from qserve_b200._lib import check, lib
+    from qserve_b200.decode import MODELS, DecodeRunner
+    from qserve_b200.engine import Engine
+    from qserve_b200.hybrid import HybridDecoder, StepBatch, random_weights
+    from qserve_b200.modelcfg import AttentionMixerConfig, DeltaMixerConfig, HybridConfig, HybridLayerConfig, MlpConfig, ModelConfig, RotaryConfig
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    hbm_gbs, peak_src = peaks()[0], peaks()[1] if len(peaks()) > 1 else "measured"
+    try:
+        tflops = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["bf16_tflops"]
+    except (OSError, KeyError, ValueError):
+        tflops = 1590.0
+    stream = torch.cuda.current_stream()
+    reps = max(3, args.kernel_reps)
+    B, CTX, NP, LP = 64, 1024, 4, 2048
+    out = {"metric": "hybrid decoder throughput (tokens/s, random weights, bf16, 4 layers)", "unit": "tokens/s", "impl": "ours", "dtype": "bf16",
+           "data": "synthetic", "peaks": {"hbm_gbs": hbm_gbs, "bf16_tflops": tflops}, "sizes": {}}
+    for name, (W, H, G, D, FF, V) in HYBRID_SIZES.items():
+        att = AttentionMixerConfig(H, G, D, D, RotaryConfig(D // 2, 1e6, 4.0, 4096, 32.0, 1.0), D ** -0.5, maps=2, diff=0.5, head_norm=True)
+        dlt = DeltaMixerConfig(H, G, D, D, 4)
+        cfg = HybridConfig("Rizurax", V, W, 1e-5, tuple(HybridLayerConfig(t, m, MlpConfig("dense", FF)) for t, m in
+                                                       (("attention", att), ("delta", dlt), ("attention", att), ("delta", dlt))),
+                           pair_buckets=4093, pair_mul_prev=127, pair_mul_cur=7)
+        model = HybridDecoder(cfg, random_weights(cfg, 0, dev), torch.bfloat16, dev)
+        eng = Engine(model, max_tokens=B * (CTX + 64), max_seqs=B)
+        g = torch.Generator().manual_seed(0)
+        rec = {}
+        with torch.no_grad():
+            # ---- prefill: NP prompts of LP tokens in one step
+            prompts = [torch.randint(0, V, (LP,), generator=g).tolist() for _ in range(NP)]
+            for i, p in enumerate(prompts):
+                eng.cache.admit(("p", i)); eng.cache.reserve(("p", i), LP)
+            rows = [(eng.cache.seqs[("p", i)].slot, 0, -1, p) for i, p in enumerate(prompts)]
+            pb = StepBatch.build(rows, eng.cache.sync_block_table(), dev)
+            t = time_kernel(lambda: (model.forward(pb, eng.cache), 1)[1], reps, stream)
+            rec["prefill"] = {"tokens": NP * LP, "ms": t * 1e3, "tokens_per_s": NP * LP / t}
+            kern = {}
+            ly_a, ly_d = model.layers[0], model.layers[1]
+            T = NP * LP
+            proj_a = torch.randn(T, ly_a.mixer.in_features, device=dev).to(torch.bfloat16)
+            proj_d = torch.randn(T, ly_d.mixer.in_features, device=dev).to(torch.bfloat16)
+            cat = torch.empty(T, H * D + FF, dtype=torch.bfloat16, device=dev)
+            scratch = torch.empty(ly_d.mixer.scratch_floats(T), dtype=torch.float32, device=dev)
+            s = torch.cuda.current_stream().cuda_stream
+            raw = lambda: torch._C._cuda_getCurrentRawStream(0)
+            ta = time_kernel(lambda: (ly_a.mixer.run(proj_a, cat, pb, eng.cache.runs[0], 64, None, 0, raw()), 2)[1], reps, stream) * 2
+            flops = H * NP * (LP * (LP + 1) // 2) * (2 * 2 * D + 2 * 2 * D)
+            kern["attention_prefill(rope+append+attention)"] = {"us": ta * 1e6, "tflops": flops / ta / 1e12, "frac_of_measured_bf16_peak": flops / ta / 1e12 / tflops}
+            td = time_kernel(lambda: (ly_d.mixer.run(proj_d, cat, pb, eng.cache.runs[1], 64, scratch, 0, raw()), 1)[1], reps, stream)
+            kern["delta_prefill(conv+scan+gate)"] = {"us": td * 1e6, "tokens_per_s": T / td}
+            x = torch.randn(T, W, device=dev)
+            h1, h2 = torch.empty(T, W, dtype=torch.bfloat16, device=dev), torch.empty(T, W, dtype=torch.bfloat16, device=dev)
+            tn = time_kernel(lambda: (check(lib.qs_hyb_rms_norm(h1.data_ptr(), h2.data_ptr(), x.data_ptr(), ly_a.norm1.data_ptr(), ly_a.norm2.data_ptr(),
+                                                                 1.0, 1e-5, T, W, 0, raw())), 1)[1], reps, stream)
+            kern["rms_norm_dual"] = {"us": tn * 1e6, "frac_of_measured_hbm": T * W * 8 / tn / 1e9 / hbm_gbs}
+            gu = torch.randn(T, 2 * FF, device=dev).to(torch.bfloat16)
+            tg = time_kernel(lambda: (check(lib.qs_hyb_gelu_tanh_mul(cat.data_ptr(), cat.stride(0), gu.data_ptr(), T, FF, 0, raw())), 1)[1], reps, stream)
+            kern["gelu_tanh_mul"] = {"us": tg * 1e6, "frac_of_measured_hbm": T * FF * 6 / tg / 1e9 / hbm_gbs}
+            for i in range(NP):
+                eng.release(("p", i))
+            # ---- decode: B sequences with CTX tokens of context, one token each
+            for i in range(B):
+                eng.cache.admit(("d", i)); eng.cache.reserve(("d", i), CTX + 1)
+            rows = [(eng.cache.seqs[("d", i)].slot, CTX, 5, [int(torch.randint(0, V, (1,), generator=g))]) for i in range(B)]
+            db = StepBatch.build(rows, eng.cache.sync_block_table(), dev)
+            t = time_kernel(lambda: (model.logits(model.forward(db, eng.cache)), 1)[1], reps * 4, stream)
+            rec["decode"] = {"batch": B, "ctx": CTX, "ms": t * 1e3, "tokens_per_s": B / t}
+            ta = time_kernel(lambda: (ly_a.mixer.run(proj_a[:B], cat[:B], db, eng.cache.runs[0], 64, None, 0, raw()), 2)[1], reps * 4, stream) * 2
+            kvb = B * (CTX + 1) * G * (2 * D + D) * 2
+            kern["attention_decode(rope+append+attention)"] = {"us": ta * 1e6, "frac_of_measured_hbm": kvb / ta / 1e9 / hbm_gbs}
+            td = time_kernel(lambda: (ly_d.mixer.run(proj_d[:B], cat[:B], db, eng.cache.runs[1], 64, scratch, 0, raw()), 1)[1], reps * 4, stream)
+            kern["delta_decode(conv+scan+gate)"] = {"us": td * 1e6, "frac_of_measured_hbm": B * H * D * D * 8 / td / 1e9 / hbm_gbs}
+            rec["kernels"] = kern
+        del eng, model
+        torch.cuda.empty_cache()
+        # ---- the closest existing model at equal size: Llama-style W4A8KV4 (4 layers), decode step and its attention kernels
+        key = "bench-" + name
+        MODELS[key] = ModelConfig(key, W, FF, H, G, 4, V, 1e6, head_dim=D)
+        with torch.no_grad():
+            run = DecodeRunner(key, "w4a8kv4", B, CTX, dev)
+            run.capture()
+            t = time_kernel(lambda: (run.step(), 1)[1], reps * 4, stream, graph=False)
+            peer = {"decode": {"batch": B, "ctx": CTX, "ms": t * 1e3, "tokens_per_s": B / t}}
+            run.qkv_buf.normal_()
+            ta = time_kernel(lambda: (run._attention(0), 1)[1], reps * 4, stream)
+            peer["attention_decode_kv4"] = {"us": ta * 1e6, "frac_of_measured_hbm": run.kv_bytes_per_step() / run.L / ta / 1e9 / hbm_gbs}
+            q = torch.randn(NP * LP, H, D, device=dev).half()
+            k = torch.randn(NP * LP, G, D, device=dev).half()
+            cu = torch.arange(0, NP * LP + 1, LP, dtype=torch.int32, device=dev)
+            tp = time_kernel(lambda: (backend.flash_attn_varlen_func(q, k, k, cu, cu, LP, LP, 0.0, None, True), 1)[1], reps, stream)
+            fl = H * NP * (LP * (LP + 1) // 2) * 4 * D
+            peer["attention_prefill_fp16"] = {"us": tp * 1e6, "tflops": fl / tp / 1e12, "frac_of_measured_bf16_peak": fl / tp / 1e12 / tflops}
+            del run
+        torch.cuda.empty_cache()
+        rec["llama_w4a8kv4_equal_size"] = peer
+        out["sizes"][name] = rec
+    print(json.dumps(out), flush=True)
+
+
+# ------------------------------------------------------------------------------------------------------------
 def main():
     args = parse()
     rank = int(os.environ.get("RANK", "0"))
@@ -635,6 +754,10 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
         reference_arm(args, rank)
+        return
+    if args.hybrid:
+        if rank == 0:
+            hybrid_block(args)
         return
     if args.impl == "reference-gpu":
         if rank == 0:

@@ -226,7 +226,7 @@ class HybridDecoder:
         x = torch.empty((T, W), dtype=torch.float32, device=dev)
         check(lib.qs_hyb_embed(x.data_ptr(), _p(b.tokens), _p(b.prev), self.embed.data_ptr(), _p(self.pair), T, W, cfg.pair_buckets,
                                cfg.pair_mul_prev, cfg.pair_mul_cur, dt, s))
-        need = max(ly.mixer.scratch_floats(T) for ly in self.layers)
+        need = max((ly.mixer.scratch_floats(T) for ly in self.layers), default=0)
         if need and (self._scratch is None or self._scratch.numel() < need):
             self._scratch = torch.empty(need, dtype=torch.float32, device=dev)
         h1 = torch.empty((T, W), dtype=self.dtype, device=dev)
@@ -255,3 +255,37 @@ class HybridDecoder:
         check(lib.qs_hyb_rms_norm(h.data_ptr(), None, x_rows.data_ptr(), self.final_norm.data_ptr(), None, self.cfg.norm_offset, self.cfg.eps, n, W,
                                   self.dt, _stream(self.device)))
         return torch.mm(h, self.head.t()).float()
+
+
+def random_weights(cfg: HybridConfig, seed: int = 0, device: Optional[torch.device] = None, dtype: torch.dtype = torch.bfloat16) -> Dict[str, torch.Tensor]:
+    """Random weights of the design's tensor names and shapes (benchmarks and smoke tests: there is no network for checkpoints), scaled so
+    that activations stay O(1)."""
+    g = torch.Generator(device=device or "cpu")
+    g.manual_seed(seed)
+    W = cfg.width
+
+    def r(*shape, s=1.0):
+        return (torch.randn(*shape, generator=g, device=device) * s).to(dtype)
+
+    w = {"embed": r(cfg.vocab, W), "head": r(cfg.vocab, W, s=W ** -0.5), "final.norm": r(W, s=0.1)}
+    if cfg.pair_buckets:
+        w["bigram"] = r(cfg.pair_buckets + 1, W, s=0.5)
+    for i, ly in enumerate(cfg.layers):
+        p, m = f"l{i}.", ly.mixer
+        H, G, D, Dv = m.heads, m.kv_heads, m.dim, m.vdim
+        w[p + "norm1"] = r(W, s=0.1)
+        if isinstance(m, AttentionMixerConfig):
+            w[p + "mix.q"], w[p + "mix.k"], w[p + "mix.v"] = r(H * m.maps * D, W, s=W ** -0.5), r(G * m.maps * D, W, s=W ** -0.5), r(G * Dv, W, s=W ** -0.5)
+            for n in ("lq1", "lk1", "lq2", "lk2"):
+                w[p + "mix." + n] = r(D, s=0.1)
+        else:
+            w[p + "mix.q"], w[p + "mix.k"], w[p + "mix.v"] = r(G * D, W, s=W ** -0.5), r(G * D, W, s=W ** -0.5), r(H * Dv, W, s=W ** -0.5)
+            for n, c in (("q", G * D), ("k", G * D), ("v", H * Dv)):
+                w[p + f"mix.{n}.conv"] = r(c, m.conv, s=0.5)
+            w[p + "mix.b"], w[p + "mix.a"], w[p + "mix.g"] = r(H, W, s=W ** -0.5), r(H, W, s=W ** -0.5), r(H * Dv, W, s=W ** -0.5)
+            w[p + "mix.A_log"], w[p + "mix.dt_bias"], w[p + "mix.norm"] = r(H, s=0.5), r(H, s=0.5), 1.0 + r(Dv, s=0.1)
+        w[p + "mix.o"] = r(W, H * Dv, s=(H * Dv) ** -0.5)
+        if ly.mlp is not None:
+            w[p + "norm2"] = r(W, s=0.1)
+            w[p + "mlp.gate"], w[p + "mlp.up"], w[p + "mlp.down"] = r(ly.mlp.ff, W, s=W ** -0.5), r(ly.mlp.ff, W, s=W ** -0.5), r(W, ly.mlp.ff, s=ly.mlp.ff ** -0.5)
+    return w

@@ -32,12 +32,16 @@ def silu(z):
     return z * torch.sigmoid(z)
 
 
-def embed_tokens(tokens, table, bigram, buckets: int, mul_prev: int, mul_cur: int):
-    """Token embedding plus a hashed (previous, current) pair embedding; a sequence's first token takes the table's last row."""
+def embed_tokens(tokens, table, bigram=None, buckets: int = 0, mul_prev: int = 0, mul_cur: int = 0):
+    """Token embedding plus (if there is a pair table) a hashed (previous, current) pair embedding; a sequence's first token takes the
+    table's last row."""
     rows = []
     for i, t in enumerate(tokens):
-        row = buckets if i == 0 else (tokens[i - 1] * mul_prev + t * mul_cur) % buckets
-        rows.append(table[t].to(F) + bigram[row].to(F))
+        x = table[t].to(F)
+        if bigram is not None:
+            row = buckets if i == 0 else (tokens[i - 1] * mul_prev + t * mul_cur) % buckets
+            x = x + bigram[row].to(F)
+        rows.append(x)
     return torch.stack(rows)
 
 
@@ -150,8 +154,11 @@ def layer_schedule(cfg: dict):
 def forward(cfg: dict, weights: dict, tokens, return_layers: bool = False):
     """Logits [T, vocab] (float64) of one whole sequence; optionally the residual stream after every layer run."""
     eps = cfg["norm"]["eps"]
-    bg = cfg["embedding"]["bigram"]
-    x = embed_tokens(list(tokens), weights["embed"], weights["bigram"], bg["buckets"], bg["mul_prev"], bg["mul_cur"])
+    bg = (cfg.get("embedding") or {}).get("bigram")
+    if bg:
+        x = embed_tokens(list(tokens), weights["embed"], weights["bigram"], bg["buckets"], bg["mul_prev"], bg["mul_cur"])
+    else:
+        x = embed_tokens(list(tokens), weights["embed"])
     trace = []
     for li in layer_schedule(cfg):
         spec = cfg["layers"][li]
