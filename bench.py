@@ -689,10 +689,10 @@ def hybrid_block(args):
             proj_a = torch.randn(T, ly_a.mixer.in_features, device=dev).to(torch.bfloat16)
             proj_d = torch.randn(T, ly_d.mixer.in_features, device=dev).to(torch.bfloat16)
             cat = torch.empty(T, H * D + FF, dtype=torch.bfloat16, device=dev)
-            scratch = torch.empty(ly_d.mixer.scratch_floats(T), dtype=torch.float32, device=dev)
+            scratch = torch.empty(max(ly_d.mixer.scratch_floats(T), ly_a.mixer.scratch_floats(T)), dtype=torch.float32, device=dev)
             s = torch.cuda.current_stream().cuda_stream
             raw = lambda: torch._C._cuda_getCurrentRawStream(0)
-            ta = time_kernel(lambda: (ly_a.mixer.run(proj_a, cat, pb, eng.cache.runs[0], 64, None, 0, raw()), 2)[1], reps, stream) * 2
+            ta = time_kernel(lambda: (ly_a.mixer.run(proj_a, cat, pb, eng.cache.runs[0], 64, scratch, 0, raw()), 1)[1], reps, stream)
             flops = H * NP * (LP * (LP + 1) // 2) * (2 * 2 * D + 2 * 2 * D)
             kern["attention_prefill(rope+append+attention)"] = {"us": ta * 1e6, "tflops": flops / ta / 1e12, "frac_of_measured_bf16_peak": flops / ta / 1e12 / tflops}
             td = time_kernel(lambda: (ly_d.mixer.run(proj_d, cat, pb, eng.cache.runs[1], 64, scratch, 0, raw()), 1)[1], reps, stream)
@@ -714,7 +714,7 @@ def hybrid_block(args):
             db = StepBatch.build(rows, eng.cache.sync_block_table(), dev)
             t = time_kernel(lambda: (model.logits(model.forward(db, eng.cache)), 1)[1], reps * 4, stream)
             rec["decode"] = {"batch": B, "ctx": CTX, "ms": t * 1e3, "tokens_per_s": B / t}
-            ta = time_kernel(lambda: (ly_a.mixer.run(proj_a[:B], cat[:B], db, eng.cache.runs[0], 64, None, 0, raw()), 2)[1], reps * 4, stream) * 2
+            ta = time_kernel(lambda: (ly_a.mixer.run(proj_a[:B], cat[:B], db, eng.cache.runs[0], 64, scratch, 0, raw()), 1)[1], reps * 4, stream)
             kvb = B * (CTX + 1) * G * (2 * D + D) * 2
             kern["attention_decode(rope+append+attention)"] = {"us": ta * 1e6, "frac_of_measured_hbm": kvb / ta / 1e9 / hbm_gbs}
             td = time_kernel(lambda: (ly_d.mixer.run(proj_d[:B], cat[:B], db, eng.cache.runs[1], 64, scratch, 0, raw()), 1)[1], reps * 4, stream)

@@ -233,6 +233,18 @@ QS_API int qs_hyb_attention(void* out, int64_t out_stride, const void* q, int64_
                             const int32_t* tok_slot, const int32_t* tok_pos, const int32_t* block_table, int max_blocks, int tokens_n,
                             int heads, int kv_heads, int maps, int dim, int vdim, float scale, float lambda, float out_scale, float eps,
                             int head_norm, int page_size, int dtype, void* stream);
+/* The same attention on the fast kernels (bfloat16 storage, dim and vdim multiples of 16, vdim in {32, 64, 96, 128, 256}, heads / kv_heads <= 16):
+ * entries of at least 16 tokens run as 64-row tiles on the tensor cores (tile_entry / tile_row0: entry and first row within it of every tile;
+ * long_tokens: their token rows; scratch fp32 [tokens, heads, maps, vdim]), the tokens listed in short_tokens on the vectorised single-token
+ * kernel.  qs_hyb_attention_fast_supported returns 1 if the shape qualifies. */
+QS_API int qs_hyb_attention_fast_supported(int dtype, int heads, int kv_heads, int maps, int dim, int vdim, int64_t q_stride);
+QS_API int qs_hyb_attention_fast(void* out, int64_t out_stride, const void* q, int64_t q_stride, const void* kpool, const void* vpool,
+                                 const int32_t* tok_slot, const int32_t* tok_pos, const int32_t* block_table, int max_blocks,
+                                 const int32_t* tile_entry, const int32_t* tile_row0, int n_tiles, const int32_t* long_tokens, int n_long,
+                                 const int32_t* short_tokens, int n_short, const int32_t* entry_start, const int32_t* entry_len,
+                                 const int32_t* entry_slot, const int32_t* entry_pos0, float* scratch, int heads, int kv_heads, int maps, int dim,
+                                 int vdim, float scale, float lambda, float out_scale, float eps, int head_norm, int page_size, int dtype,
+                                 void* stream);
 /* gated delta rule over projection rows [G*dim q | G*dim k | H*vdim v | H*vdim gate | H b | H a]: short convolution (taps) + silu on
  * q | k | v, unit q (times dim^-1/2) and k, beta = sigmoid(b), decay = exp(-exp(a_log) softplus(a + dt_bias)), then per head
  * S <- decay S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q; out = o * rsqrt(mean(o^2) + eps) * norm_w * silu(gate).

@@ -296,6 +296,336 @@ __global__ void __launch_bounds__(kAttnThreads) paged_multimap_attention_kernel(
 }
 
 // ---------------------------------------------------------------------------------------------------------------------------------
+// Prompt portions on the tensor cores (bfloat16 storage).  One block = 64 consecutive query rows of one entry x one (head, map); keys are
+// walked in tiles of 64 positions through the block table.  S = Q K^T with mma.sync m16n8k16 (bf16 operands are exact, fp32 accumulation: the
+// scores are fp32), online softmax in fp32 registers, and P V with the fp32 weights split into PSPLIT bfloat16 terms (p = hi + mid + lo, 24
+// mantissa bits) so that the weights enter the product at fp32 precision although the tensor cores take 16-bit operands.  The normalised
+// per-map outputs go to an fp32 scratch [token][head][map][Dv]; multimap_combine_kernel finishes the head.
+// ---------------------------------------------------------------------------------------------------------------------------------
+constexpr int kTileQ = 64, kTileK = 64, kPad = 8;
+
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t (&r)[4], const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+template <int NVT, int PSPLIT>  // NVT = Dv / 16
+__global__ void __launch_bounds__(128) tile_attention_kernel(
+    float* __restrict__ a_out, const __nv_bfloat16* __restrict__ q, long long q_stride, const __nv_bfloat16* __restrict__ kpool,
+    const __nv_bfloat16* __restrict__ vpool, const int* __restrict__ tile_entry, const int* __restrict__ tile_row0,
+    const int* __restrict__ entry_start, const int* __restrict__ entry_len, const int* __restrict__ entry_slot, const int* __restrict__ entry_pos0,
+    const int* __restrict__ block_table, int max_blocks, int H, int G, int maps, int D, float scale, int page) {
+  extern __shared__ __align__(16) unsigned char smraw[];
+  constexpr int Dv = NVT * 16;
+  const int SD = D + kPad, SV = Dv + kPad;
+  __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smraw);
+  __nv_bfloat16* Ks = Qs + kTileQ * SD;
+  __nv_bfloat16* Vs = Ks + kTileK * SD;
+  const int tile = blockIdx.x, hm = blockIdx.y, h = hm / maps, m = hm - h * maps, g = h / (H / G);
+  const int e = tile_entry[tile], r0 = tile_row0[tile];
+  const int n_rows = min(kTileQ, entry_len[e] - r0);
+  const int tok0 = entry_start[e] + r0, qpos0 = entry_pos0[e] + r0;
+  const int* bt = block_table + (size_t)entry_slot[e] * max_blocks;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int dch = D >> 3;  // 16-byte chunks per q / k row
+  for (int c = tid; c < kTileQ * dch; c += 128) {
+    const int r = c / dch, cc = c - r * dch;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (r < n_rows) v = *reinterpret_cast<const uint4*>(q + (size_t)(tok0 + r) * q_stride + (size_t)(h * maps + m) * D + cc * 8);
+    *reinterpret_cast<uint4*>(Qs + r * SD + cc * 8) = v;
+  }
+  float o[2 * NVT][4];
+#pragma unroll
+  for (int i = 0; i < 2 * NVT; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+  const int last_qpos = qpos0 + n_rows - 1;
+  const int n_kt = last_qpos / kTileK + 1;
+  const int qrow = warp * 16 + (lane >> 2);  // this thread's rows: qrow, qrow + 8
+  for (int kt = 0; kt < n_kt; ++kt) {
+    __syncthreads();
+    for (int c = tid; c < kTileK * dch; c += 128) {
+      const int r = c / dch, cc = c - r * dch, kp = kt * kTileK + r;
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (kp <= last_qpos) v = *reinterpret_cast<const uint4*>(kpool + ((((size_t)bt[kp / page] * page + kp % page) * G + g) * maps + m) * (size_t)D + cc * 8);
+      *reinterpret_cast<uint4*>(Ks + r * SD + cc * 8) = v;
+    }
+    for (int c = tid; c < kTileK * (Dv / 8); c += 128) {
+      const int r = c / (Dv / 8), cc = c - r * (Dv / 8), kp = kt * kTileK + r;
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (kp <= last_qpos) v = *reinterpret_cast<const uint4*>(vpool + (((size_t)bt[kp / page] * page + kp % page) * G + g) * (size_t)Dv + cc * 8);
+      *reinterpret_cast<uint4*>(Vs + r * SV + cc * 8) = v;
+    }
+    __syncthreads();
+    float s[8][4];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+    for (int ks = 0; ks < D; ks += 16) {
+      uint32_t a[4];
+      ldsm_x4(a, Qs + (warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * SD + ks + (lane >> 4) * 8);
+#pragma unroll
+      for (int np = 0; np < 4; ++np) {
+        uint32_t b[4];
+        ldsm_x4(b, Ks + (np * 16 + (lane & 7) + (lane >> 4) * 8) * SD + ks + ((lane >> 3) & 1) * 8);
+        mma_bf16(s[2 * np], a, b[0], b[1]);
+        mma_bf16(s[2 * np + 1], a, b[2], b[3]);
+      }
+    }
+    // scale, causal mask, online softmax (rows qrow and qrow + 8; a row's 64 columns live in the 4 lanes of a quad)
+    float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int kpos = kt * kTileK + nt * 8 + (lane & 3) * 2 + (j & 1);
+        const int qp = qpos0 + qrow + (j >> 1) * 8;
+        const float v = kpos <= qp ? s[nt][j] * scale : -INFINITY;
+        s[nt][j] = v;
+        mx[j >> 1] = fmaxf(mx[j >> 1], v);
+      }
+    float corr[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+      mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+      const float m_new = fmaxf(m_run[r], mx[r]);
+      corr[r] = m_new == -INFINITY ? 1.f : expf(m_run[r] - m_new);
+      m_run[r] = m_new;
+      l_run[r] *= corr[r];
+    }
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float mm = m_run[j >> 1];
+        const float p = mm == -INFINITY ? 0.f : expf(s[nt][j] - mm);
+        s[nt][j] = p;
+        l_run[j >> 1] += p;
+      }
+#pragma unroll
+    for (int i = 0; i < 2 * NVT; ++i) {
+      o[i][0] *= corr[0]; o[i][1] *= corr[0]; o[i][2] *= corr[1]; o[i][3] *= corr[1];
+    }
+#pragma unroll
+    for (int kk = 0; kk < 4; ++kk) {  // 16 keys per step
+      uint32_t a[PSPLIT][4];
+#pragma unroll
+      for (int part = 0; part < 4; ++part) {
+        const int nt = 2 * kk + (part >> 1), j0 = (part & 1) * 2;
+        float r0v = s[nt][j0], r1v = s[nt][j0 + 1];
+#pragma unroll
+        for (int sp = 0; sp < PSPLIT; ++sp) {
+          const __nv_bfloat16 h0 = __float2bfloat16_rn(r0v), h1 = __float2bfloat16_rn(r1v);
+          __nv_bfloat162 pr;
+          pr.x = h0; pr.y = h1;
+          a[sp][part] = *reinterpret_cast<uint32_t*>(&pr);
+          r0v -= __bfloat162float(h0);
+          r1v -= __bfloat162float(h1);
+        }
+      }
+#pragma unroll
+      for (int nv = 0; nv < NVT; ++nv) {
+        uint32_t b[4];
+        ldsm_x4_trans(b, Vs + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * SV + nv * 16 + (lane >> 4) * 8);
+#pragma unroll
+        for (int sp = 0; sp < PSPLIT; ++sp) {
+          mma_bf16(o[2 * nv], a[sp], b[0], b[1]);
+          mma_bf16(o[2 * nv + 1], a[sp], b[2], b[3]);
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
+    l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
+  }
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    const int row = qrow + r * 8;
+    if (row < n_rows) {
+      const float inv = 1.f / l_run[r];
+      float* dst = a_out + (((size_t)(tok0 + row) * H + h) * maps + m) * (size_t)Dv + (lane & 3) * 2;
+#pragma unroll
+      for (int i = 0; i < 2 * NVT; ++i) *reinterpret_cast<float2*>(dst + i * 8) = make_float2(o[i][2 * r] * inv, o[i][2 * r + 1] * inv);
+    }
+  }
+}
+
+// finish a head from its per-map outputs: o = a1 [- lambda a2]; (head_norm) unit RMS; times out_scale.  One warp per (listed token, head).
+template <typename ST>
+__global__ void multimap_combine_kernel(ST* __restrict__ out, long long out_stride, const float* __restrict__ a_in, const int* __restrict__ tok_list,
+                                        int n_list, int H, int maps, int Dv, float lambda, float out_scale, float eps, int head_norm) {
+  const int w = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  if (w >= n_list * H) return;
+  const int t = tok_list[w / H], h = w % H;
+  const float* a = a_in + ((size_t)t * H + h) * maps * (size_t)Dv;
+  float ss = 0.f;
+  for (int i = lane; i < Dv; i += 32) {
+    const float v = maps == 2 ? a[i] - lambda * a[Dv + i] : a[i];
+    ss += v * v;
+  }
+  ss = warp_sum(ss);
+  const float r = head_norm ? out_scale / sqrtf(ss / (float)Dv + eps) : out_scale;
+  ST* dst = out + (size_t)t * out_stride + (size_t)h * Dv;
+  for (int i = lane; i < Dv; i += 32) stf(dst + i, (maps == 2 ? a[i] - lambda * a[Dv + i] : a[i]) * r);
+}
+
+// ---------------------------------------------------------------------------------------------------------------------------------
+// Single tokens and short portions (bfloat16 storage, 16-byte loads).  One block per (listed token, kv head); warp w serves query head
+// g * R + w % R of the group (R = H / G) and, when a block has more warps than the group has heads, a share of the keys; the warps of a group
+// walk the same key / value rows at about the same time, so a row comes from HBM once.  A warp handles KPI keys per iteration: all 32 lanes
+// score each key (16-byte chunks of the [map 1 | map 2] row, warp-reduced per map), then LPK lanes per key accumulate the weighted value
+// chunk for every map.  Each warp keeps its own running maximum and sum; partials are merged through shared memory, then the head is
+// finished as in multimap_combine_kernel.
+// ---------------------------------------------------------------------------------------------------------------------------------
+template <int MAPS>
+__global__ void decode_vec_attention_kernel(__nv_bfloat16* __restrict__ out, long long out_stride, const __nv_bfloat16* __restrict__ q, long long q_stride,
+                                            const __nv_bfloat16* __restrict__ kpool, const __nv_bfloat16* __restrict__ vpool,
+                                            const int* __restrict__ tok_list, const int* __restrict__ tok_slot, const int* __restrict__ tok_pos,
+                                            const int* __restrict__ block_table, int max_blocks, int H, int G, int D, int Dv, int wph, float scale,
+                                            float lambda, float out_scale, float eps, int head_norm, int page) {
+  extern __shared__ float smf[];
+  const int R = H / G, nw = blockDim.x >> 5;
+  const int t = tok_list[blockIdx.x], g = blockIdx.y;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int hl = warp % R, part = warp / R;  // head within the group, share of the keys
+  const int h = g * R + hl;
+  const int pos = tok_pos[t];
+  const int* bt = block_table + (size_t)tok_slot[t] * max_blocks;
+  float* qs = smf;                          // [R][MAPS * D]
+  float* mrg = qs + R * MAPS * D;           // [nw][MAPS][2 + Dv]
+  for (int i = threadIdx.x; i < R * MAPS * D; i += blockDim.x) qs[i] = __bfloat162float(q[(size_t)t * q_stride + (size_t)(g * R) * MAPS * D + i]);
+  __syncthreads();
+  const float* qh = qs + hl * MAPS * D;
+  const int kch = (MAPS * D) >> 3, vch = Dv >> 3;
+  const int lpk = vch <= 16 ? 16 : 32, kpi = 32 / lpk;
+  const int sub = lane / lpk, vc = lane % lpk;
+  float m_run[MAPS], l_run[MAPS], acc[MAPS][8];
+#pragma unroll
+  for (int mm = 0; mm < MAPS; ++mm) {
+    m_run[mm] = -INFINITY; l_run[mm] = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[mm][j] = 0.f;
+  }
+  const int n_keys = pos + 1;
+  for (int k0 = part * kpi; k0 < n_keys; k0 += wph * kpi) {
+    float sc[2][MAPS];
+    uint4 vv = make_uint4(0, 0, 0, 0);
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+#pragma unroll
+      for (int mm = 0; mm < MAPS; ++mm) sc[u][mm] = -INFINITY;
+      const int kj = k0 + u;
+      if (u < kpi && kj < n_keys) {
+        const size_t cell = (size_t)bt[kj / page] * page + kj % page;
+        if (sub == u && vc < vch) vv = *reinterpret_cast<const uint4*>(vpool + (cell * G + g) * (size_t)Dv + vc * 8);
+        const __nv_bfloat16* kr = kpool + (cell * G + g) * (size_t)(MAPS * D);
+        float d[MAPS];
+#pragma unroll
+        for (int mm = 0; mm < MAPS; ++mm) d[mm] = 0.f;
+        for (int c = lane; c < kch; c += 32) {
+          const uint4 kv = *reinterpret_cast<const uint4*>(kr + c * 8);
+          const __nv_bfloat162* k2 = reinterpret_cast<const __nv_bfloat162*>(&kv);
+          const float* qq = qh + c * 8;
+          float a = 0.f;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float2 f = __bfloat1622float2(k2[j]);
+            a += qq[2 * j] * f.x + qq[2 * j + 1] * f.y;
+          }
+          if (MAPS == 1 || c * 8 < D) d[0] += a; else d[MAPS - 1] += a;
+        }
+#pragma unroll
+        for (int mm = 0; mm < MAPS; ++mm) sc[u][mm] = warp_sum(d[mm]) * scale;
+      }
+    }
+    float p[MAPS];
+#pragma unroll
+    for (int mm = 0; mm < MAPS; ++mm) {
+      const float m_new = fmaxf(m_run[mm], fmaxf(sc[0][mm], sc[1][mm]));
+      const float corr = expf(m_run[mm] - m_new);
+      const float p0 = expf(sc[0][mm] - m_new), p1 = expf(sc[1][mm] - m_new);
+      l_run[mm] = l_run[mm] * corr + p0 + p1;
+      m_run[mm] = m_new;
+      p[mm] = sub == 0 ? p0 : p1;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[mm][j] *= corr;
+    }
+    const __nv_bfloat162* v2 = reinterpret_cast<const __nv_bfloat162*>(&vv);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 f = __bfloat1622float2(v2[j]);
+#pragma unroll
+      for (int mm = 0; mm < MAPS; ++mm) {
+        acc[mm][2 * j] += p[mm] * f.x;
+        acc[mm][2 * j + 1] += p[mm] * f.y;
+      }
+    }
+  }
+  // the two key lanes-groups of a warp hold partial sums over different keys with the same running maximum
+  if (kpi == 2) {
+#pragma unroll
+    for (int mm = 0; mm < MAPS; ++mm)
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[mm][j] += __shfl_xor_sync(0xffffffffu, acc[mm][j], 16);
+  }
+  float* mine = mrg + (size_t)warp * MAPS * (2 + Dv);
+#pragma unroll
+  for (int mm = 0; mm < MAPS; ++mm) {
+    if (lane == 0) { mine[mm * (2 + Dv)] = m_run[mm]; mine[mm * (2 + Dv) + 1] = l_run[mm]; }
+    if (sub == 0 && vc < vch)
+#pragma unroll
+      for (int j = 0; j < 8; ++j) mine[mm * (2 + Dv) + 2 + vc * 8 + j] = acc[mm][j];
+  }
+  __syncthreads();
+  if (part != 0) return;
+  // warp `hl` finishes its head: merge the wph partials, combine the maps, normalise
+  float ss = 0.f;
+  float ov[8];  // Dv <= 256: 8 values per lane
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const int i = lane + 32 * j;
+    ov[j] = 0.f;
+    if (i < Dv) {
+      float am[MAPS];
+#pragma unroll
+      for (int mm = 0; mm < MAPS; ++mm) {
+        float mx = -INFINITY;
+        for (int pp = 0; pp < wph; ++pp) mx = fmaxf(mx, mrg[(size_t)(pp * R + hl) * MAPS * (2 + Dv) + mm * (2 + Dv)]);
+        float num = 0.f, den = 0.f;
+        for (int pp = 0; pp < wph; ++pp) {
+          const float* w = mrg + (size_t)(pp * R + hl) * MAPS * (2 + Dv) + mm * (2 + Dv);
+          const float f = expf(w[0] - mx);  // a share without keys has maximum -inf and weighs 0
+          num += f * w[2 + i];
+          den += f * w[1];
+        }
+        am[mm] = num / den;
+      }
+      ov[j] = MAPS == 2 ? am[0] - lambda * am[MAPS - 1] : am[0];
+      ss += ov[j] * ov[j];
+    }
+  }
+  ss = warp_sum(ss);
+  const float r = head_norm ? out_scale / sqrtf(ss / (float)Dv + eps) : out_scale;
+  __nv_bfloat16* dst = out + (size_t)t * out_stride + (size_t)h * Dv;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const int i = lane + 32 * j;
+    if (i < Dv) dst[i] = __float2bfloat16_rn(ov[j] * r);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------------------------------
 // gated delta rule, step 1: per token, short causal convolution + silu over the q | k | v channels (taps before the portion come from
 // the sequence's convolution state, taps before the sequence's start are zero), unit-length q (times D^-1/2) and k per head, the write
 // strength beta = sigmoid(b) and the decay exp(-exp(A_log) softplus(a + dt_bias)) per head.  All fp32 from the projections on.
@@ -463,6 +793,30 @@ int launch_attention(void* out, long long out_stride, const void* q, long long q
   return check_cuda(cudaGetLastError(), "hyb_attention");
 }
 
+
+bool fast_attention_supported(int dtype, int heads, int kv_heads, int maps, int dim, int vdim, long long q_stride) {
+  if (dtype != QS_DTYPE_BF16 || (maps != 1 && maps != 2) || kv_heads <= 0 || heads % kv_heads != 0) return false;
+  const int nvt = vdim / 16, R = heads / kv_heads;
+  if (dim % 16 != 0 || vdim % 16 != 0 || !(nvt == 2 || nvt == 4 || nvt == 6 || nvt == 8 || nvt == 16)) return false;
+  if (R > 16 || dim > 512 || q_stride % 8 != 0) return false;
+  return true;
+}
+
+template <int NVT>
+int launch_tiles(float* scratch, const void* q, long long q_stride, const void* kpool, const void* vpool, const int* tile_entry, const int* tile_row0,
+                 int n_tiles, const int* entry_start, const int* entry_len, const int* entry_slot, const int* entry_pos0, const int* block_table,
+                 int max_blocks, int H, int G, int maps, int D, float scale, int page, cudaStream_t s) {
+  const size_t smem = ((size_t)2 * kTileQ * (D + kPad) + (size_t)kTileK * (NVT * 16 + kPad)) * sizeof(__nv_bfloat16);
+  static bool attr_set[kMaxDevices] = {};
+  if (smem > 48 * 1024 && !attr_set[device_ordinal()]) {
+    if (int rc = check_cuda(cudaFuncSetAttribute(tile_attention_kernel<NVT, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024), "tile attention smem")) return rc;
+    attr_set[device_ordinal()] = true;
+  }
+  tile_attention_kernel<NVT, 3><<<dim3(n_tiles, H * maps), 128, smem, s>>>(scratch, (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)kpool,
+      (const __nv_bfloat16*)vpool, tile_entry, tile_row0, entry_start, entry_len, entry_slot, entry_pos0, block_table, max_blocks, H, G, maps, D, scale, page);
+  return check_cuda(cudaGetLastError(), "hyb_attention tiles");
+}
+
 template <typename ST>
 int launch_delta(void* out, long long out_stride, float* prep, float* o_raw, const void* proj, long long stride, const float* conv_w,
                  float* conv_state, float* state, const float* a_log, const float* dt_bias, const float* norm_w, const int* tok_entry,
@@ -581,6 +935,55 @@ int qs_hyb_attention(void* out, int64_t out_stride, const void* q, int64_t q_str
                                                heads, kv_heads, maps, dim, vdim, scale, lambda, out_scale, eps, head_norm, page_size, s),
         return launch_attention<float>(out, out_stride, q, q_stride, kpool, vpool, tok_slot, tok_pos, block_table, max_blocks, tokens_n, heads,
                                        kv_heads, maps, dim, vdim, scale, lambda, out_scale, eps, head_norm, page_size, s));
+}
+
+int qs_hyb_attention_fast_supported(int dtype, int heads, int kv_heads, int maps, int dim, int vdim, int64_t q_stride) {
+  return fast_attention_supported(dtype, heads, kv_heads, maps, dim, vdim, q_stride) ? 1 : 0;
+}
+
+int qs_hyb_attention_fast(void* out, int64_t out_stride, const void* q, int64_t q_stride, const void* kpool, const void* vpool,
+                          const int32_t* tok_slot, const int32_t* tok_pos, const int32_t* block_table, int max_blocks, const int32_t* tile_entry,
+                          const int32_t* tile_row0, int n_tiles, const int32_t* long_tokens, int n_long, const int32_t* short_tokens, int n_short,
+                          const int32_t* entry_start, const int32_t* entry_len, const int32_t* entry_slot, const int32_t* entry_pos0,
+                          float* scratch, int heads, int kv_heads, int maps, int dim, int vdim, float scale, float lambda, float out_scale, float eps,
+                          int head_norm, int page_size, int dtype, void* stream) {
+  QS_REQUIRE(out && q && kpool && vpool && tok_slot && tok_pos && block_table, "hyb_attention_fast: null tensor");
+  QS_REQUIRE(fast_attention_supported(dtype, heads, kv_heads, maps, dim, vdim, q_stride), "hyb_attention_fast: shape not supported (use qs_hyb_attention)");
+  QS_REQUIRE(n_tiles == 0 || (tile_entry && tile_row0 && long_tokens && scratch && entry_start && entry_len && entry_slot && entry_pos0),
+             "hyb_attention_fast: null tile table");
+  QS_REQUIRE(n_short == 0 || short_tokens, "hyb_attention_fast: null token list");
+  cudaStream_t s = (cudaStream_t)stream;
+  if (n_tiles > 0) {
+    int rc = 0;
+#define QS_TILES(NVT) rc = launch_tiles<NVT>(scratch, q, q_stride, kpool, vpool, tile_entry, tile_row0, n_tiles, entry_start, entry_len, entry_slot, \
+                                             entry_pos0, block_table, max_blocks, heads, kv_heads, maps, dim, scale, page_size, s)
+    switch (vdim / 16) {
+      case 2: QS_TILES(2); break;
+      case 4: QS_TILES(4); break;
+      case 6: QS_TILES(6); break;
+      case 8: QS_TILES(8); break;
+      default: QS_TILES(16); break;
+    }
+#undef QS_TILES
+    if (rc) return rc;
+    const int warps = n_long * heads;
+    multimap_combine_kernel<__nv_bfloat16><<<(warps + 3) / 4, 128, 0, s>>>((__nv_bfloat16*)out, out_stride, scratch, long_tokens, n_long, heads, maps, vdim,
+                                                                          lambda, out_scale, eps, head_norm);
+  }
+  if (n_short > 0) {
+    const int R = heads / kv_heads, wph = R >= 4 ? 1 : 4 / R, nw = R * wph;
+    const size_t smem = ((size_t)R * maps * dim + (size_t)nw * maps * (2 + vdim)) * sizeof(float);
+    dim3 grid(n_short, kv_heads);
+    if (maps == 2)
+      decode_vec_attention_kernel<2><<<grid, nw * 32, smem, s>>>((__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)kpool,
+          (const __nv_bfloat16*)vpool, short_tokens, tok_slot, tok_pos, block_table, max_blocks, heads, kv_heads, dim, vdim, wph, scale, lambda, out_scale,
+          eps, head_norm, page_size);
+    else
+      decode_vec_attention_kernel<1><<<grid, nw * 32, smem, s>>>((__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)kpool,
+          (const __nv_bfloat16*)vpool, short_tokens, tok_slot, tok_pos, block_table, max_blocks, heads, kv_heads, dim, vdim, wph, scale, lambda, out_scale,
+          eps, head_norm, page_size);
+  }
+  return check_cuda(cudaGetLastError(), "hyb_attention_fast");
 }
 
 int qs_hyb_gated_delta(void* out, int64_t out_stride, float* prep, float* o_raw, const void* proj, int64_t stride, const float* conv_w,

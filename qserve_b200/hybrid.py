@@ -47,16 +47,29 @@ class StepBatch:
     entry_slot: torch.Tensor   # int32 [E]
     entry_pos0: torch.Tensor   # int32 [E] position of the entry's first token
     block_table: torch.Tensor  # int32 [slots, max_blocks]
+    # attention work lists: entries of at least TILE_MIN tokens are cut into tiles of TILE_ROWS query rows, the other tokens run one by one
+    n_tiles: int = 0
+    n_long: int = 0
+    n_short: int = 0
+    tile_entry: Optional[torch.Tensor] = None    # int32 [n_tiles] entry of the tile
+    tile_row0: Optional[torch.Tensor] = None     # int32 [n_tiles] first row of the tile within its entry
+    long_tokens: Optional[torch.Tensor] = None   # int32 [n_long] rows covered by tiles
+    short_tokens: Optional[torch.Tensor] = None  # int32 [n_short] all other rows
+
+    TILE_MIN = 16
+    TILE_ROWS = 64
 
     @staticmethod
     def build(entries: Sequence[tuple], block_table: torch.Tensor, device: torch.device) -> "StepBatch":
         """entries: (slot, first position, previous token or -1, token list) per sequence, in batch order."""
         T = sum(len(e[3]) for e in entries)
         E = len(entries)
-        host = torch.empty(5 * T + 4 * E, dtype=torch.int32)
-        tok, prev, slot, pos, ent = (host[i * T:(i + 1) * T] for i in range(5))
-        es, el, eslot, ep0 = (host[5 * T + i * E: 5 * T + (i + 1) * E] for i in range(4))
-        r = 0
+        tiles = [(i, r0) for i, e in enumerate(entries) if len(e[3]) >= StepBatch.TILE_MIN for r0 in range(0, len(e[3]), StepBatch.TILE_ROWS)]
+        nt = len(tiles)
+        host = torch.empty(6 * T + 4 * E + 2 * nt, dtype=torch.int32)
+        tok, prev, slot, pos, ent, lists = (host[i * T:(i + 1) * T] for i in range(6))
+        es, el, eslot, ep0 = (host[6 * T + i * E: 6 * T + (i + 1) * E] for i in range(4))
+        r, longs, shorts = 0, [], []
         for i, (s, p0, last, toks) in enumerate(entries):
             n = len(toks)
             if n == 0:
@@ -69,12 +82,18 @@ class StepBatch:
             pos[r:r + n] = torch.arange(p0, p0 + n, dtype=torch.int32)
             ent[r:r + n] = i
             es[i], el[i], eslot[i], ep0[i] = r, n, s, p0
+            (longs if n >= StepBatch.TILE_MIN else shorts).extend(range(r, r + n))
             r += n
+        lists[:] = torch.tensor(longs + shorts, dtype=torch.int32)
+        if nt:
+            host[6 * T + 4 * E:] = torch.tensor([t[0] for t in tiles] + [t[1] for t in tiles], dtype=torch.int32)
         if device.type == "cuda":
             host = host.pin_memory()
         d = host.to(device, non_blocking=True)
-        v = [d[i * T:(i + 1) * T] for i in range(5)] + [d[5 * T + i * E: 5 * T + (i + 1) * E] for i in range(4)]
-        return StepBatch(T, E, *v, block_table)
+        v = [d[i * T:(i + 1) * T] for i in range(5)] + [d[6 * T + i * E: 6 * T + (i + 1) * E] for i in range(4)]
+        o = 6 * T + 4 * E
+        return StepBatch(T, E, *v, block_table, nt, len(longs), len(shorts), d[o:o + nt], d[o + nt:o + 2 * nt], d[5 * T:5 * T + len(longs)],
+                         d[5 * T + len(longs):6 * T])
 
 
 # ------------------------------------------------------------------------------------------------------------------------
@@ -104,13 +123,23 @@ class MultiMapAttentionMixer:
             self.lam, self.out_scale = 0.0, 1.0
 
     def scratch_floats(self, tokens: int) -> int:
-        return 0
+        return tokens * self.m.heads * self.m.maps * self.m.vdim  # per-map outputs of the tiled prompt kernel
 
     def run(self, proj: torch.Tensor, out: torch.Tensor, b: StepBatch, run_cache: dict, page_size: int, scratch, dt: int, stream) -> None:
         m = self.m
+        fast = scratch is not None and lib.qs_hyb_attention_fast_supported(dt, m.heads, m.kv_heads, m.maps, m.dim, m.vdim, proj.stride(0)) == 1
         check(lib.qs_hyb_rope_append(proj.data_ptr(), proj.stride(0), _p(b.tok_slot), _p(b.tok_pos), _p(b.block_table), b.block_table.shape[1],
                                      run_cache["k"].data_ptr(), run_cache["v"].data_ptr(), self.inv_freq.data_ptr(), self.amp, b.n_tokens,
                                      m.heads, m.kv_heads, m.maps, m.dim, m.vdim, m.rot.dims, page_size, dt, stream))
+        if fast:
+            # prompt portions as 64-row tiles on the tensor cores, single tokens and short portions on the vectorised kernel
+            check(lib.qs_hyb_attention_fast(out.data_ptr(), out.stride(0), proj.data_ptr(), proj.stride(0), run_cache["k"].data_ptr(),
+                                            run_cache["v"].data_ptr(), _p(b.tok_slot), _p(b.tok_pos), _p(b.block_table), b.block_table.shape[1],
+                                            _p(b.tile_entry), _p(b.tile_row0), b.n_tiles, _p(b.long_tokens), b.n_long, _p(b.short_tokens), b.n_short,
+                                            _p(b.entry_start), _p(b.entry_len), _p(b.entry_slot), _p(b.entry_pos0), scratch.data_ptr(), m.heads,
+                                            m.kv_heads, m.maps, m.dim, m.vdim, m.scale, self.lam, self.out_scale, self.eps,
+                                            1 if m.head_norm else 0, page_size, dt, stream))
+            return
         check(lib.qs_hyb_attention(out.data_ptr(), out.stride(0), proj.data_ptr(), proj.stride(0), run_cache["k"].data_ptr(),
                                    run_cache["v"].data_ptr(), _p(b.tok_slot), _p(b.tok_pos), _p(b.block_table), b.block_table.shape[1],
                                    b.n_tokens, m.heads, m.kv_heads, m.maps, m.dim, m.vdim, m.scale, self.lam, self.out_scale, self.eps,

@@ -215,6 +215,62 @@ def test_one_key_stands_out(dev, needle, decode):
     assert row_err(got, want) < F32_TOL
 
 
+@pytest.mark.parametrize("needle", [0, 63, 64, 128, 300, 510])
+@pytest.mark.parametrize("decode", [False, True])
+def test_one_key_stands_out_on_the_fast_kernels(dev, needle, decode):
+    """The same in bfloat16 with head sizes the tensor-core prompt kernel and the vectorised single-token kernel take."""
+    n = 512
+    cfg, w, toks = _needle_model(n, needle, dim=16, vdim=32)
+    want = O.forward(cfg, w, toks)[-1:]
+    eng = _engine(cfg, w, torch.bfloat16)
+    if decode:
+        eng.step([("a", toks[:-1], [])])
+        got = eng.step([("a", toks[-1:], [0])])
+    else:
+        eng.step([("a", toks[:100], [])])
+        got = eng.step([("a", toks[100:], [n - 101])])
+    assert row_err(got, want) < 0.05
+
+
+@pytest.mark.parametrize("shape", [(4, 2, 2, 16, 32), (4, 4, 2, 48, 96), (8, 2, 2, 32, 64), (2, 1, 1, 64, 128), (3, 3, 2, 16, 256), (16, 1, 2, 16, 32)],
+                         ids=lambda s: "H%d-G%d-maps%d-D%d-Dv%d" % s)
+def test_fast_attention_kernels_match_the_plain_kernel(dev, shape):
+    """Same bfloat16 inputs and cache through the tensor-core / vectorised kernels and through the plain kernel: prompt portions with and
+    without context, portions that end inside a page, short portions and single tokens in one batch."""
+    from qserve_b200.hybrid import MultiMapAttentionMixer, StepBatch
+    from qserve_b200.modelcfg import AttentionMixerConfig, RotaryConfig
+
+    H, G, maps, D, Dv = shape
+    m = AttentionMixerConfig(H, G, D, Dv, RotaryConfig(8, 100.0), D ** -0.5, maps=maps, diff=0.3 if maps == 2 else 0.0, head_norm=maps == 2)
+    g = torch.Generator().manual_seed(5)
+    r = lambda *s: torch.randn(*s, generator=g)
+    w = {"q": r(H * maps * D, 8), "k": r(G * maps * D, 8), "v": r(G * Dv, 8), "o": r(8, H * Dv)}
+    for n in ("lq1", "lk1", "lq2", "lk2"):
+        w[n] = r(D) * 0.3
+    mixer = MultiMapAttentionMixer(m, w, 1e-5, torch.bfloat16, dev)
+    pages, page = 40, 64
+    kpool = torch.zeros(pages, page, G, maps * D, dtype=torch.bfloat16, device=dev)
+    vpool = torch.zeros(pages, page, G, Dv, dtype=torch.bfloat16, device=dev)
+    table = torch.randperm(pages, generator=g).to(torch.int32).view(4, 10).to(dev)
+    # step 1: context; step 2: continuation of every sequence with another portion size
+    steps = [[(0, 0, -1, [0] * 200), (1, 0, -1, [0] * 70), (2, 0, -1, [0] * 3), (3, 0, -1, [0] * 16)],
+             [(0, 200, 0, [0] * 1), (1, 70, 0, [0] * 130), (2, 3, 0, [0] * 15), (3, 16, 0, [0] * 64)],
+             [(0, 201, 0, [0] * 90), (1, 200, 0, [0] * 1), (2, 18, 0, [0] * 1), (3, 80, 0, [0] * 17)]]
+    for entries in steps:
+        b = StepBatch.build(entries, table, dev)
+        T = b.n_tokens
+        proj = (r(T, mixer.in_features) * 1.5).to(torch.bfloat16).to(dev)
+        outs = []
+        for fast in (True, False):
+            p2, out = proj.clone(), torch.zeros(T, H * Dv, dtype=torch.bfloat16, device=dev)
+            scratch = torch.empty(mixer.scratch_floats(T), dtype=torch.float32, device=dev) if fast else None
+            mixer.run(p2, out, b, {"k": kpool, "v": vpool}, page, scratch, 0, torch.cuda.current_stream().cuda_stream)
+            outs.append(out.float())
+        torch.cuda.synchronize()
+        d = (outs[0] - outs[1]).abs()
+        assert float(d.max()) <= 2.0 ** -6 * float(outs[1].abs().max()) and float(d.mean()) < 1e-3 * float(outs[1].abs().mean())
+
+
 def test_delta_state_remembers_an_early_token(dev):
     """A recurrent layer with decay close to one: what the first token wrote is still read hundreds of tokens later."""
     cfg = make_config([delta_layer(heads=2, kv_heads=1, dim=16, vdim=16, conv=2, ff=0)])
