@@ -11,6 +11,8 @@
 #include <cuda_bf16.h>
 #include <math.h>
 
+#include <algorithm>
+
 #include "../../include/qserve_b200.h"
 #include "common.cuh"
 #include "launch.h"
@@ -314,6 +316,9 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], 
   asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+__device__ __forceinline__ void cp_async16(void* dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
+}
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
@@ -330,7 +335,7 @@ __global__ void __launch_bounds__(128) tile_attention_kernel(
   const int SD = D + kPad, SV = Dv + kPad;
   __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smraw);
   __nv_bfloat16* Ks = Qs + kTileQ * SD;
-  __nv_bfloat16* Vs = Ks + kTileK * SD;
+  __nv_bfloat16* Vs = Ks + 2 * kTileK * SD;  // two key buffers, then two value buffers
   const int tile = blockIdx.x, hm = blockIdx.y, h = hm / maps, m = hm - h * maps, g = h / (H / G);
   const int e = tile_entry[tile], r0 = tile_row0[tile];
   const int n_rows = min(kTileQ, entry_len[e] - r0);
@@ -351,21 +356,33 @@ __global__ void __launch_bounds__(128) tile_attention_kernel(
   const int last_qpos = qpos0 + n_rows - 1;
   const int n_kt = last_qpos / kTileK + 1;
   const int qrow = warp * 16 + (lane >> 2);  // this thread's rows: qrow, qrow + 8
-  for (int kt = 0; kt < n_kt; ++kt) {
-    __syncthreads();
+  // key / value tiles are double-buffered: tile kt + 1 streams in with cp.async while tile kt is multiplied
+  auto load_kv = [&](int kt, int buf) {
+    __nv_bfloat16* Kd = Ks + (size_t)buf * kTileK * SD;
+    __nv_bfloat16* Vd = Vs + (size_t)buf * kTileK * SV;
     for (int c = tid; c < kTileK * dch; c += 128) {
       const int r = c / dch, cc = c - r * dch, kp = kt * kTileK + r;
-      uint4 v = make_uint4(0, 0, 0, 0);
-      if (kp <= last_qpos) v = *reinterpret_cast<const uint4*>(kpool + ((((size_t)bt[kp / page] * page + kp % page) * G + g) * maps + m) * (size_t)D + cc * 8);
-      *reinterpret_cast<uint4*>(Ks + r * SD + cc * 8) = v;
+      if (kp <= last_qpos) cp_async16(Kd + r * SD + cc * 8, kpool + ((((size_t)bt[kp / page] * page + kp % page) * G + g) * maps + m) * (size_t)D + cc * 8);
+      else *reinterpret_cast<uint4*>(Kd + r * SD + cc * 8) = make_uint4(0, 0, 0, 0);
     }
     for (int c = tid; c < kTileK * (Dv / 8); c += 128) {
       const int r = c / (Dv / 8), cc = c - r * (Dv / 8), kp = kt * kTileK + r;
-      uint4 v = make_uint4(0, 0, 0, 0);
-      if (kp <= last_qpos) v = *reinterpret_cast<const uint4*>(vpool + (((size_t)bt[kp / page] * page + kp % page) * G + g) * (size_t)Dv + cc * 8);
-      *reinterpret_cast<uint4*>(Vs + r * SV + cc * 8) = v;
+      if (kp <= last_qpos) cp_async16(Vd + r * SV + cc * 8, vpool + (((size_t)bt[kp / page] * page + kp % page) * G + g) * (size_t)Dv + cc * 8);
+      else *reinterpret_cast<uint4*>(Vd + r * SV + cc * 8) = make_uint4(0, 0, 0, 0);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  load_kv(0, 0);
+  for (int kt = 0; kt < n_kt; ++kt) {
+    if (kt + 1 < n_kt) {
+      load_kv(kt + 1, (kt + 1) & 1);
+      asm volatile("cp.async.wait_group 1;" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
     }
     __syncthreads();
+    const __nv_bfloat16* Kc = Ks + (size_t)(kt & 1) * kTileK * SD;
+    const __nv_bfloat16* Vc = Vs + (size_t)(kt & 1) * kTileK * SV;
     float s[8][4];
 #pragma unroll
     for (int i = 0; i < 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
@@ -375,7 +392,7 @@ __global__ void __launch_bounds__(128) tile_attention_kernel(
 #pragma unroll
       for (int np = 0; np < 4; ++np) {
         uint32_t b[4];
-        ldsm_x4(b, Ks + (np * 16 + (lane & 7) + (lane >> 4) * 8) * SD + ks + ((lane >> 3) & 1) * 8);
+        ldsm_x4(b, Kc + (np * 16 + (lane & 7) + (lane >> 4) * 8) * SD + ks + ((lane >> 3) & 1) * 8);
         mma_bf16(s[2 * np], a, b[0], b[1]);
         mma_bf16(s[2 * np + 1], a, b[2], b[3]);
       }
@@ -435,7 +452,7 @@ __global__ void __launch_bounds__(128) tile_attention_kernel(
 #pragma unroll
       for (int nv = 0; nv < NVT; ++nv) {
         uint32_t b[4];
-        ldsm_x4_trans(b, Vs + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * SV + nv * 16 + (lane >> 4) * 8);
+        ldsm_x4_trans(b, Vc + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * SV + nv * 16 + (lane >> 4) * 8);
 #pragma unroll
         for (int sp = 0; sp < PSPLIT; ++sp) {
           mma_bf16(o[2 * nv], a[sp], b[0], b[1]);
@@ -443,6 +460,7 @@ __global__ void __launch_bounds__(128) tile_attention_kernel(
         }
       }
     }
+    __syncthreads();  // every warp is done with this buffer before tile kt + 2 streams into it
   }
 #pragma unroll
   for (int r = 0; r < 2; ++r) {
@@ -488,28 +506,35 @@ __global__ void multimap_combine_kernel(ST* __restrict__ out, long long out_stri
 // chunk for every map.  Each warp keeps its own running maximum and sum; partials are merged through shared memory, then the head is
 // finished as in multimap_combine_kernel.
 // ---------------------------------------------------------------------------------------------------------------------------------
-template <int MAPS>
-__global__ void decode_vec_attention_kernel(__nv_bfloat16* __restrict__ out, long long out_stride, const __nv_bfloat16* __restrict__ q, long long q_stride,
+constexpr int kDecKeys = 4;   // keys a warp handles per iteration
+
+// QCH: 16-byte chunks of the [map 1 | map 2] key row per lane (maps * dim <= 256 QCH)
+template <int MAPS, int QCH>
+__global__ void __launch_bounds__(512) decode_vec_attention_kernel(__nv_bfloat16* __restrict__ out, long long out_stride, const __nv_bfloat16* __restrict__ q, long long q_stride,
                                             const __nv_bfloat16* __restrict__ kpool, const __nv_bfloat16* __restrict__ vpool,
                                             const int* __restrict__ tok_list, const int* __restrict__ tok_slot, const int* __restrict__ tok_pos,
                                             const int* __restrict__ block_table, int max_blocks, int H, int G, int D, int Dv, int wph, float scale,
                                             float lambda, float out_scale, float eps, int head_norm, int page) {
-  extern __shared__ float smf[];
-  const int R = H / G, nw = blockDim.x >> 5;
+  extern __shared__ float smf[];  // merge space [warps][MAPS][2 + Dv]
+  const int R = H / G;
   const int t = tok_list[blockIdx.x], g = blockIdx.y;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int hl = warp % R, part = warp / R;  // head within the group, share of the keys
   const int h = g * R + hl;
   const int pos = tok_pos[t];
   const int* bt = block_table + (size_t)tok_slot[t] * max_blocks;
-  float* qs = smf;                          // [R][MAPS * D]
-  float* mrg = qs + R * MAPS * D;           // [nw][MAPS][2 + Dv]
-  for (int i = threadIdx.x; i < R * MAPS * D; i += blockDim.x) qs[i] = __bfloat162float(q[(size_t)t * q_stride + (size_t)(g * R) * MAPS * D + i]);
-  __syncthreads();
-  const float* qh = qs + hl * MAPS * D;
   const int kch = (MAPS * D) >> 3, vch = Dv >> 3;
-  const int lpk = vch <= 16 ? 16 : 32, kpi = 32 / lpk;
+  const int lpk = vch <= 16 ? 16 : 32, kpi = 32 / lpk;  // lanes per key in the value phase, keys per value pass
   const int sub = lane / lpk, vc = lane % lpk;
+  // this lane's query chunks stay in registers, pre-multiplied by scale * log2(e): scores come out in the exp2 domain
+  float qr[QCH][8];
+  const float qscale = scale * 1.4426950408889634f;
+#pragma unroll
+  for (int i = 0; i < QCH; ++i) {
+    const int c = lane + 32 * i;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) qr[i][j] = c < kch ? __bfloat162float(q[(size_t)t * q_stride + (size_t)h * MAPS * D + c * 8 + j]) * qscale : 0.f;
+  }
   float m_run[MAPS], l_run[MAPS], acc[MAPS][8];
 #pragma unroll
   for (int mm = 0; mm < MAPS; ++mm) {
@@ -518,68 +543,84 @@ __global__ void decode_vec_attention_kernel(__nv_bfloat16* __restrict__ out, lon
     for (int j = 0; j < 8; ++j) acc[mm][j] = 0.f;
   }
   const int n_keys = pos + 1;
-  for (int k0 = part * kpi; k0 < n_keys; k0 += wph * kpi) {
-    float sc[2][MAPS];
-    uint4 vv = make_uint4(0, 0, 0, 0);
+  for (int k0 = part * kDecKeys; k0 < n_keys; k0 += wph * kDecKeys) {
+    // all loads of the iteration first: the key chunks of four keys and this lane's value chunks
+    uint4 kv[kDecKeys][QCH], vv[kDecKeys];
 #pragma unroll
-    for (int u = 0; u < 2; ++u) {
+    for (int u = 0; u < kDecKeys; ++u) {
+      const int kj = min(k0 + u, n_keys - 1);  // clamped: a key beyond the end is loaded again and masked below
+      const size_t cell = (size_t)bt[kj / page] * page + kj % page;
+      const __nv_bfloat16* kr = kpool + (cell * G + g) * (size_t)(MAPS * D);
 #pragma unroll
-      for (int mm = 0; mm < MAPS; ++mm) sc[u][mm] = -INFINITY;
-      const int kj = k0 + u;
-      if (u < kpi && kj < n_keys) {
-        const size_t cell = (size_t)bt[kj / page] * page + kj % page;
-        if (sub == u && vc < vch) vv = *reinterpret_cast<const uint4*>(vpool + (cell * G + g) * (size_t)Dv + vc * 8);
-        const __nv_bfloat16* kr = kpool + (cell * G + g) * (size_t)(MAPS * D);
-        float d[MAPS];
+      for (int i = 0; i < QCH; ++i)
+        if (lane + 32 * i < kch) kv[u][i] = *reinterpret_cast<const uint4*>(kr + (lane + 32 * i) * 8);
+      vv[u] = make_uint4(0, 0, 0, 0);
+      if ((u % kpi) == sub && vc < vch) vv[u] = *reinterpret_cast<const uint4*>(vpool + (cell * G + g) * (size_t)Dv + vc * 8);
+    }
+    float sc[kDecKeys][MAPS];
 #pragma unroll
-        for (int mm = 0; mm < MAPS; ++mm) d[mm] = 0.f;
-        for (int c = lane; c < kch; c += 32) {
-          const uint4 kv = *reinterpret_cast<const uint4*>(kr + c * 8);
-          const __nv_bfloat162* k2 = reinterpret_cast<const __nv_bfloat162*>(&kv);
-          const float* qq = qh + c * 8;
+    for (int u = 0; u < kDecKeys; ++u) {
+      float d[MAPS];
+#pragma unroll
+      for (int mm = 0; mm < MAPS; ++mm) d[mm] = 0.f;
+#pragma unroll
+      for (int i = 0; i < QCH; ++i) {
+        const int c = lane + 32 * i;
+        if (c < kch) {
+          const __nv_bfloat162* k2 = reinterpret_cast<const __nv_bfloat162*>(&kv[u][i]);
           float a = 0.f;
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
             const float2 f = __bfloat1622float2(k2[j]);
-            a += qq[2 * j] * f.x + qq[2 * j + 1] * f.y;
+            a += qr[i][2 * j] * f.x + qr[i][2 * j + 1] * f.y;
           }
           if (MAPS == 1 || c * 8 < D) d[0] += a; else d[MAPS - 1] += a;
         }
-#pragma unroll
-        for (int mm = 0; mm < MAPS; ++mm) sc[u][mm] = warp_sum(d[mm]) * scale;
       }
+#pragma unroll
+      for (int mm = 0; mm < MAPS; ++mm) sc[u][mm] = k0 + u < n_keys ? warp_sum(d[mm]) : -INFINITY;
     }
-    float p[MAPS];
 #pragma unroll
     for (int mm = 0; mm < MAPS; ++mm) {
-      const float m_new = fmaxf(m_run[mm], fmaxf(sc[0][mm], sc[1][mm]));
-      const float corr = expf(m_run[mm] - m_new);
-      const float p0 = expf(sc[0][mm] - m_new), p1 = expf(sc[1][mm] - m_new);
-      l_run[mm] = l_run[mm] * corr + p0 + p1;
-      m_run[mm] = m_new;
-      p[mm] = sub == 0 ? p0 : p1;
+      float mx = sc[0][mm];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) acc[mm][j] *= corr;
+      for (int u = 1; u < kDecKeys; ++u) mx = fmaxf(mx, sc[u][mm]);
+      if (mx > m_run[mm]) {  // warp-uniform: the running maximum moves, rescale what has been gathered
+        const float corr = exp2f(m_run[mm] - mx);
+        l_run[mm] *= corr;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[mm][j] *= corr;
+        m_run[mm] = mx;
+      }
+#pragma unroll
+      for (int u = 0; u < kDecKeys; ++u) {
+        const float p = exp2f(sc[u][mm] - m_run[mm]);
+        l_run[mm] += p;
+        sc[u][mm] = p;
+      }
     }
-    const __nv_bfloat162* v2 = reinterpret_cast<const __nv_bfloat162*>(&vv);
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const float2 f = __bfloat1622float2(v2[j]);
+    for (int u = 0; u < kDecKeys; ++u) {
+      const __nv_bfloat162* v2 = reinterpret_cast<const __nv_bfloat162*>(&vv[u]);  // zeros where this lane does not serve key u
 #pragma unroll
-      for (int mm = 0; mm < MAPS; ++mm) {
-        acc[mm][2 * j] += p[mm] * f.x;
-        acc[mm][2 * j + 1] += p[mm] * f.y;
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = __bfloat1622float2(v2[j]);
+#pragma unroll
+        for (int mm = 0; mm < MAPS; ++mm) {
+          acc[mm][2 * j] += sc[u][mm] * f.x;
+          acc[mm][2 * j + 1] += sc[u][mm] * f.y;
+        }
       }
     }
   }
-  // the two key lanes-groups of a warp hold partial sums over different keys with the same running maximum
+  // the lane groups of a warp hold partial sums over different keys with the same running maximum
   if (kpi == 2) {
 #pragma unroll
     for (int mm = 0; mm < MAPS; ++mm)
 #pragma unroll
       for (int j = 0; j < 8; ++j) acc[mm][j] += __shfl_xor_sync(0xffffffffu, acc[mm][j], 16);
   }
-  float* mine = mrg + (size_t)warp * MAPS * (2 + Dv);
+  float* mine = smf + (size_t)warp * MAPS * (2 + Dv);
 #pragma unroll
   for (int mm = 0; mm < MAPS; ++mm) {
     if (lane == 0) { mine[mm * (2 + Dv)] = m_run[mm]; mine[mm * (2 + Dv) + 1] = l_run[mm]; }
@@ -601,11 +642,11 @@ __global__ void decode_vec_attention_kernel(__nv_bfloat16* __restrict__ out, lon
 #pragma unroll
       for (int mm = 0; mm < MAPS; ++mm) {
         float mx = -INFINITY;
-        for (int pp = 0; pp < wph; ++pp) mx = fmaxf(mx, mrg[(size_t)(pp * R + hl) * MAPS * (2 + Dv) + mm * (2 + Dv)]);
+        for (int pp = 0; pp < wph; ++pp) mx = fmaxf(mx, smf[(size_t)(pp * R + hl) * MAPS * (2 + Dv) + mm * (2 + Dv)]);
         float num = 0.f, den = 0.f;
         for (int pp = 0; pp < wph; ++pp) {
-          const float* w = mrg + (size_t)(pp * R + hl) * MAPS * (2 + Dv) + mm * (2 + Dv);
-          const float f = expf(w[0] - mx);  // a share without keys has maximum -inf and weighs 0
+          const float* w = smf + (size_t)(pp * R + hl) * MAPS * (2 + Dv) + mm * (2 + Dv);
+          const float f = exp2f(w[0] - mx);  // a share without keys has maximum -inf and weighs 0
           num += f * w[2 + i];
           den += f * w[1];
         }
@@ -700,61 +741,112 @@ __global__ void delta_conv_state_kernel(float* __restrict__ conv_state, const ST
   for (int i = 0; i < keep; ++i) st[(size_t)i * C + c] = tmp[i];
 }
 
-// step 2: the recurrence.  One block per (entry, head); thread d owns column d of the head's [D, Dv] state in registers (D <= DP).
-// Per token, in this order:  S <- decay S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q.
-template <int DP>
-__global__ void delta_scan_kernel(float* __restrict__ o_raw, const float* __restrict__ prep, float* __restrict__ state,
-                                  const int* __restrict__ entry_start, const int* __restrict__ entry_len, const int* __restrict__ entry_slot,
-                                  const int* __restrict__ entry_pos0, int H, int G, int D, int Dv) {
-  __shared__ float qk[2][2 * DP];
-  const int e = blockIdx.x, h = blockIdx.y, g = h / (H / G);
-  const int d = threadIdx.x;
+// step 2: the recurrence.  Columns of a head's [D, Dv] state are independent, so a block owns 128 / PARTS columns of one (entry, head):
+// thread (column, part) keeps rows [part Q, (part + 1) Q) of its column in registers (Q = DP / PARTS, D <= DP); the parts of a column sit in
+// adjacent lanes and meet through shuffles.  With PARTS = 1 every lane of a warp reads the same q / k words from shared memory (a
+// broadcast).  Tokens are staged CH at a time (q | k | v of the block's columns | beta | decay) with cp.async into a double buffer, so that no
+// global load sits on the token-to-token dependency chain.  Per token, in this order:
+//   S <- decay S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q.
+__device__ __forceinline__ void cp_async4(float* dst, const float* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
+}
+template <int PARTS>
+__device__ __forceinline__ float part_sum(float v) {
+#pragma unroll
+  for (int o = 1; o < PARTS; o <<= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+template <int DP, int PARTS, int CH>
+__global__ void __launch_bounds__(128) delta_scan_kernel(float* __restrict__ o_raw, const float* __restrict__ prep, float* __restrict__ state,
+                                                         const int* __restrict__ entry_start, const int* __restrict__ entry_len,
+                                                         const int* __restrict__ entry_slot, const int* __restrict__ entry_pos0, int H, int G, int D,
+                                                         int Dv) {
+  extern __shared__ __align__(16) float sm[];  // [2][CH][ROW]
+  constexpr int Q = DP / PARTS, SEG = Q + 4, COLS = 128 / PARTS;  // a part's q / k segment is padded by 16 bytes: parts hit different banks
+  constexpr int QK = PARTS * SEG, ROW = 2 * QK + COLS + 4;
+  const int e = blockIdx.x, h = blockIdx.y, cg = blockIdx.z, g = h / (H / G);
+  const int tid = threadIdx.x, part = tid % PARTS, cl = tid / PARTS, col = cg * COLS + cl;
   const int C = 2 * G * D + H * Dv, P = C + 2 * H;
   const int n = entry_len[e], s0 = entry_start[e];
+  const bool live = col < Dv, fresh = entry_pos0[e] == 0;
   float* Sg = state + ((size_t)entry_slot[e] * H + h) * (size_t)D * Dv;
-  float S[DP];
-  const bool live = d < Dv;
-  const bool fresh = entry_pos0[e] == 0;
+  float S[Q];
 #pragma unroll
-  for (int i = 0; i < DP; ++i) S[i] = (live && !fresh && i < D) ? Sg[(size_t)i * Dv + d] : 0.f;
-  for (int i = threadIdx.x; i < 2 * DP; i += blockDim.x) {
-    const int which = i / DP, j = i - which * DP;
-    qk[0][i] = j < D ? prep[(size_t)s0 * P + (size_t)which * G * D + (size_t)g * D + j] : 0.f;
+  for (int j = 0; j < Q; ++j) {
+    const int i = part * Q + j;
+    S[j] = (live && !fresh && i < D) ? Sg[(size_t)i * Dv + col] : 0.f;
   }
-  __syncthreads();
-  for (int t = 0; t < n; ++t) {
-    const float* row = prep + (size_t)(s0 + t) * P;
-    const float* cur = qk[t & 1];
-    if (t + 1 < n) {  // stage the next token's q | k while this one is processed
-      float* nxt = qk[(t + 1) & 1];
-      for (int i = threadIdx.x; i < 2 * DP; i += blockDim.x) {
-        const int which = i / DP, j = i - which * DP;
-        nxt[i] = j < D ? row[P + (size_t)which * G * D + (size_t)g * D + j] : 0.f;
+  auto stage = [&](int chunk, int buf) {
+    for (int idx = tid; idx < CH * ROW; idx += 128) {
+      const int tk = idx / ROW, j = idx - tk * ROW, t = chunk * CH + tk;
+      float* dst = sm + (size_t)(buf * CH + tk) * ROW + j;
+      const float* src = nullptr;
+      if (t < n) {
+        const float* row = prep + (size_t)(s0 + t) * P;
+        if (j < 2 * QK) {
+          const int which = j / QK, jj = j - which * QK, pp = jj / SEG, w = jj - pp * SEG, i = pp * Q + w;  // q (which = 0) or k row i
+          if (w < Q && i < D) src = row + (size_t)(which * G + g) * D + i;
+        } else if (j < 2 * QK + COLS) {
+          const int c = cg * COLS + j - 2 * QK;
+          if (c < Dv) src = row + 2 * G * D + (size_t)h * Dv + c;
+        } else if (j == 2 * QK + COLS) {
+          src = row + C + h;
+        } else if (j == 2 * QK + COLS + 1) {
+          src = row + C + H + h;
+        }
       }
+      if (src != nullptr) cp_async4(dst, src);
+      else *dst = 0.f;
     }
-    if (live) {
-      const float decay = row[C + H + h], beta = row[C + h], v = row[2 * G * D + (size_t)h * Dv + d];
-      float kS = 0.f;
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  const int n_chunks = (n + CH - 1) / CH;
+  stage(0, 0);
+  for (int ch = 0; ch < n_chunks; ++ch) {
+    if (ch + 1 < n_chunks) {
+      stage(ch + 1, (ch + 1) & 1);
+      asm volatile("cp.async.wait_group 1;" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+    }
+    __syncthreads();
+    const int cnt = min(CH, n - ch * CH);
+    for (int tk = 0; tk < cnt; ++tk) {
+      const float* r = sm + (size_t)((ch & 1) * CH + tk) * ROW;
+      const float4* q4 = reinterpret_cast<const float4*>(r + part * SEG);
+      const float4* k4 = reinterpret_cast<const float4*>(r + QK + part * SEG);
+      const float v = r[2 * QK + cl], beta = r[2 * QK + COLS], decay = r[2 * QK + COLS + 1];
+      float kp[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int i = 0; i < DP; ++i) {
-        S[i] *= decay;
-        kS += S[i] * cur[DP + i];
+      for (int j = 0; j < Q / 4; ++j) {
+        const float4 kk = k4[j];
+        const int a = (j & 1) * 4;
+        kp[a] += S[4 * j] * kk.x; kp[a + 1] += S[4 * j + 1] * kk.y; kp[a + 2] += S[4 * j + 2] * kk.z; kp[a + 3] += S[4 * j + 3] * kk.w;
       }
+      const float kS = part_sum<PARTS>(((kp[0] + kp[1]) + (kp[2] + kp[3])) + ((kp[4] + kp[5]) + (kp[6] + kp[7]))) * decay;
       const float u = beta * (v - kS);
-      float o = 0.f;
+      float op[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int i = 0; i < DP; ++i) {
-        S[i] += cur[DP + i] * u;
-        o += S[i] * cur[i];
+      for (int j = 0; j < Q / 4; ++j) {
+        const float4 kk = k4[j], qq = q4[j];
+        const int a = (j & 1) * 4;
+        S[4 * j] = S[4 * j] * decay + kk.x * u;         op[a] += S[4 * j] * qq.x;
+        S[4 * j + 1] = S[4 * j + 1] * decay + kk.y * u; op[a + 1] += S[4 * j + 1] * qq.y;
+        S[4 * j + 2] = S[4 * j + 2] * decay + kk.z * u; op[a + 2] += S[4 * j + 2] * qq.z;
+        S[4 * j + 3] = S[4 * j + 3] * decay + kk.w * u; op[a + 3] += S[4 * j + 3] * qq.w;
       }
-      o_raw[(size_t)(s0 + t) * H * Dv + (size_t)h * Dv + d] = o;
+      const float o = part_sum<PARTS>(((op[0] + op[1]) + (op[2] + op[3])) + ((op[4] + op[5]) + (op[6] + op[7])));
+      if (part == 0 && live) o_raw[(size_t)(s0 + ch * CH + tk) * H * Dv + (size_t)h * Dv + col] = o;
     }
     __syncthreads();
   }
   if (live) {
 #pragma unroll
-    for (int i = 0; i < DP; ++i)
-      if (i < D) Sg[(size_t)i * Dv + d] = S[i];
+    for (int j = 0; j < Q; ++j) {
+      const int i = part * Q + j;
+      if (i < D) Sg[(size_t)i * Dv + col] = S[j];
+    }
   }
 }
 
@@ -798,7 +890,7 @@ bool fast_attention_supported(int dtype, int heads, int kv_heads, int maps, int 
   if (dtype != QS_DTYPE_BF16 || (maps != 1 && maps != 2) || kv_heads <= 0 || heads % kv_heads != 0) return false;
   const int nvt = vdim / 16, R = heads / kv_heads;
   if (dim % 16 != 0 || vdim % 16 != 0 || !(nvt == 2 || nvt == 4 || nvt == 6 || nvt == 8 || nvt == 16)) return false;
-  if (R > 16 || dim > 512 || q_stride % 8 != 0) return false;
+  if (R > 16 || maps * dim > 1024 || dim > 512 || q_stride % 8 != 0) return false;
   return true;
 }
 
@@ -806,7 +898,7 @@ template <int NVT>
 int launch_tiles(float* scratch, const void* q, long long q_stride, const void* kpool, const void* vpool, const int* tile_entry, const int* tile_row0,
                  int n_tiles, const int* entry_start, const int* entry_len, const int* entry_slot, const int* entry_pos0, const int* block_table,
                  int max_blocks, int H, int G, int maps, int D, float scale, int page, cudaStream_t s) {
-  const size_t smem = ((size_t)2 * kTileQ * (D + kPad) + (size_t)kTileK * (NVT * 16 + kPad)) * sizeof(__nv_bfloat16);
+  const size_t smem = ((size_t)3 * kTileQ * (D + kPad) + (size_t)2 * kTileK * (NVT * 16 + kPad)) * sizeof(__nv_bfloat16);
   static bool attr_set[kMaxDevices] = {};
   if (smem > 48 * 1024 && !attr_set[device_ordinal()]) {
     if (int rc = check_cuda(cudaFuncSetAttribute(tile_attention_kernel<NVT, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024), "tile attention smem")) return rc;
@@ -830,14 +922,20 @@ int launch_delta(void* out, long long out_stride, float* prep, float* o_raw, con
   if (taps > 1)
     delta_conv_state_kernel<ST><<<dim3((C + 127) / 128, E), 128, 0, s>>>(conv_state, (const ST*)proj, stride, entry_start, entry_len, entry_slot,
                                                                           entry_pos0, C, taps);
-  const int threads = ((Dv + 31) / 32) * 32;
-  dim3 grid(E, H);
-#define QS_SCAN(DP) delta_scan_kernel<DP><<<grid, threads, 0, s>>>(o_raw, prep, state, entry_start, entry_len, entry_slot, entry_pos0, H, G, D, Dv)
-  if (D <= 16) QS_SCAN(16);
-  else if (D <= 32) QS_SCAN(32);
-  else if (D <= 64) QS_SCAN(64);
-  else if (D <= 128) QS_SCAN(128);
-  else QS_SCAN(256);
+  // rows of a column per thread: all of them up to 64 (a warp then reads q / k as broadcasts), 64 above
+#define QS_SCAN(DP, PARTS, CH)                                                                                                                \
+  do {                                                                                                                                        \
+    constexpr int cols = 128 / PARTS;                                                                                                         \
+    const size_t sm = (size_t)2 * CH * (2 * PARTS * (DP / PARTS + 4) + cols + 4) * sizeof(float);                                             \
+    dim3 grid(E, H, (Dv + cols - 1) / cols);                                                                                                  \
+    if (sm > 48 * 1024) cudaFuncSetAttribute(delta_scan_kernel<DP, PARTS, CH>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);         \
+    delta_scan_kernel<DP, PARTS, CH><<<grid, 128, sm, s>>>(o_raw, prep, state, entry_start, entry_len, entry_slot, entry_pos0, H, G, D, Dv); \
+  } while (0)
+  if (D <= 16) QS_SCAN(16, 1, 16);
+  else if (D <= 32) QS_SCAN(32, 1, 16);
+  else if (D <= 64) QS_SCAN(64, 2, 16);
+  else if (D <= 128) QS_SCAN(128, 4, 16);
+  else QS_SCAN(256, 8, 8);
 #undef QS_SCAN
   const int warps = T * H;
   delta_gate_out_kernel<ST><<<(warps + 3) / 4, 128, 0, s>>>((ST*)out, out_stride, o_raw, (const ST*)proj, stride, norm_w, T, H, G, D, Dv, eps);
@@ -971,17 +1069,28 @@ int qs_hyb_attention_fast(void* out, int64_t out_stride, const void* q, int64_t 
                                                                           lambda, out_scale, eps, head_norm);
   }
   if (n_short > 0) {
-    const int R = heads / kv_heads, wph = R >= 4 ? 1 : 4 / R, nw = R * wph;
-    const size_t smem = ((size_t)R * maps * dim + (size_t)nw * maps * (2 + vdim)) * sizeof(float);
+    // warps per head: enough warps in flight to hide the latency of the key walk when the batch is small (about 48 per SM wanted),
+    // within 1024 threads and 48 KB of merge space per block
+    const int R = heads / kv_heads;
+    const size_t per_warp = (size_t)maps * (2 + vdim) * sizeof(float), q_bytes = 0;
+    int wph = (48 * num_sms() + n_short * heads - 1) / (n_short * heads);
+    wph = std::max(1, std::min(wph, 16 / R));  // at most 512 threads: 65 registers per thread
+    while (wph > 1 && q_bytes + (size_t)R * wph * per_warp > 48 * 1024) --wph;
+    const int nw = R * wph;
+    const size_t smem = q_bytes + (size_t)nw * per_warp;
+    QS_REQUIRE(smem <= 48 * 1024, "hyb_attention_fast: head group too large for the single-token kernel");
     dim3 grid(n_short, kv_heads);
-    if (maps == 2)
-      decode_vec_attention_kernel<2><<<grid, nw * 32, smem, s>>>((__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)kpool,
-          (const __nv_bfloat16*)vpool, short_tokens, tok_slot, tok_pos, block_table, max_blocks, heads, kv_heads, dim, vdim, wph, scale, lambda, out_scale,
-          eps, head_norm, page_size);
-    else
-      decode_vec_attention_kernel<1><<<grid, nw * 32, smem, s>>>((__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)kpool,
-          (const __nv_bfloat16*)vpool, short_tokens, tok_slot, tok_pos, block_table, max_blocks, heads, kv_heads, dim, vdim, wph, scale, lambda, out_scale,
-          eps, head_norm, page_size);
+    const int qch = (maps * dim / 8 + 31) / 32;
+#define QS_DEC(MAPS, QCH)                                                                                                                          \
+  decode_vec_attention_kernel<MAPS, QCH><<<grid, nw * 32, smem, s>>>((__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)q, q_stride,         \
+      (const __nv_bfloat16*)kpool, (const __nv_bfloat16*)vpool, short_tokens, tok_slot, tok_pos, block_table, max_blocks, heads, kv_heads, dim, \
+      vdim, wph, scale, lambda, out_scale, eps, head_norm, page_size)
+    if (maps == 2) {
+      if (qch <= 1) QS_DEC(2, 1); else if (qch <= 2) QS_DEC(2, 2); else QS_DEC(2, 4);
+    } else {
+      if (qch <= 1) QS_DEC(1, 1); else if (qch <= 2) QS_DEC(1, 2); else QS_DEC(1, 4);
+    }
+#undef QS_DEC
   }
   return check_cuda(cudaGetLastError(), "hyb_attention_fast");
 }
