@@ -699,7 +699,7 @@ def hybrid_block(args):
             kern["delta_prefill(conv+scan+gate)"] = {"us": td * 1e6, "tokens_per_s": T / td}
             x = torch.randn(T, W, device=dev)
             h1, h2 = torch.empty(T, W, dtype=torch.bfloat16, device=dev), torch.empty(T, W, dtype=torch.bfloat16, device=dev)
-            tn = time_kernel(lambda: (check(lib.qs_hyb_rms_norm(h1.data_ptr(), h2.data_ptr(), x.data_ptr(), ly_a.norm1.data_ptr(), ly_a.norm2.data_ptr(),
+            tn = time_kernel(lambda: (check(lib.qs_hyb_rms_norm(h1.data_ptr(), h2.data_ptr(), x.data_ptr(), None, ly_a.norm1.data_ptr(), ly_a.norm2.data_ptr(),
                                                                  1.0, 1e-5, T, W, 0, raw())), 1)[1], reps, stream)
             kern["rms_norm_dual"] = {"us": tn * 1e6, "frac_of_measured_hbm": T * W * 8 / tn / 1e9 / hbm_gbs}
             gu = torch.randn(T, 2 * FF, device=dev).to(torch.bfloat16)

@@ -214,9 +214,10 @@ QS_API int qs_silu_and_mul_quant(int8_t* out, const void* input, void* input_sum
 /* out[t] = table[tokens[t]] + pair_table[prev[t] < 0 ? buckets : (prev[t] * mul_prev + tokens[t] * mul_cur) % buckets]; pair_table may be NULL */
 QS_API int qs_hyb_embed(float* out, const int32_t* tokens, const int32_t* prev, const void* table, const void* pair_table, int tokens_n,
                         int width, int buckets, int64_t mul_prev, int64_t mul_cur, int dtype, void* stream);
-/* out_k = x * rsqrt(mean(x^2) + eps) * (offset + w_k), k = 1, 2 (out2 / w2 may be NULL); x fp32 [tokens, width], w fp32 */
-QS_API int qs_hyb_rms_norm(void* out1, void* out2, const float* x, const float* w1, const float* w2, float offset, float eps, int tokens_n,
-                           int width, int dtype, void* stream);
+/* [x <- x + add (storage type, may be NULL);]  out_k = x * rsqrt(mean(x^2) + eps) * (offset + w_k), k = 1, 2 (out2 / w2 may be NULL);
+ * x fp32 [tokens, width] (updated in place when add is given), w fp32 */
+QS_API int qs_hyb_rms_norm(void* out1, void* out2, float* x, const void* add, const float* w1, const float* w2, float offset, float eps,
+                           int tokens_n, int width, int dtype, void* stream);
 /* x[i] += y[i] (x fp32, y in the storage type) */
 QS_API int qs_hyb_residual_add(float* x, const void* y, int64_t n, int dtype, void* stream);
 /* out[t, i] = gelu_tanh(in[t, i]) * in[t, ff + i]; out rows of out_stride elements */

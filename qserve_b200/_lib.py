@@ -52,7 +52,7 @@ SIGNATURES = {
     "qs_dequant_silu_and_mul_quant": (c_int, [_P, _P, _F, _F, _F, _P, _P, _I, _I, _P]),
     # unquantised hybrid decoders (csrc/hybrid.cu)
     "qs_hyb_embed": (c_int, [_P, _P, _P, _P, _P, _I, _I, _I, _L, _L, _I, _P]),
-    "qs_hyb_rms_norm": (c_int, [_P, _P, _P, _P, _P, _F, _F, _I, _I, _I, _P]),
+    "qs_hyb_rms_norm": (c_int, [_P, _P, _P, _P, _P, _P, _F, _F, _I, _I, _I, _P]),
     "qs_hyb_residual_add": (c_int, [_P, _P, _L, _I, _P]),
     "qs_hyb_gelu_tanh_mul": (c_int, [_P, _L, _P, _I, _I, _I, _P]),
     "qs_hyb_rope_append": (c_int, [_P, _L, _P, _P, _P, _I, _P, _P, _P, _F, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P]),

@@ -24,7 +24,7 @@ def _engine(args, max_tokens: int):
         print("qserve_b200 needs a CUDA device (there is no CPU path)", file=sys.stderr)
         raise SystemExit(4)
     dtype = {"bfloat16": torch.bfloat16, "float32": torch.float32}[args.dtype]
-    return Engine.from_dir(args.model, dtype, max_tokens=max_tokens, max_seqs=args.max_seqs, page_size=args.page_size)
+    return Engine.from_dir(args.model, dtype, max_tokens=max_tokens, max_seqs=args.max_seqs, page_size=args.page_size, use_graphs=not args.no_graphs)
 
 
 def _common(p):
@@ -32,6 +32,7 @@ def _common(p):
     p.add_argument("--dtype", choices=("bfloat16", "float32"), default="bfloat16")
     p.add_argument("--max-seqs", type=int, default=4, help="state slots = most live sequences")
     p.add_argument("--page-size", type=int, default=64)
+    p.add_argument("--no-graphs", action="store_true", help="launch decode-only steps eagerly instead of replaying a captured CUDA graph")
 
 
 def trace_main(argv=None) -> int:

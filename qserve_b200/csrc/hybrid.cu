@@ -79,22 +79,26 @@ __global__ void embed_pair_kernel(float* __restrict__ out, const int* __restrict
 
 // ---------------------------------------------------------------------------------------------------------------------------------
 // RMS norm of the fp32 stream with one or two gains (the two branches of a parallel layer read the same normalised row):
-//   out_k = x * rsqrt(mean(x^2) + eps) * (offset + w_k)
+//   [x <- x + add;]  out_k = x * rsqrt(mean(x^2) + eps) * (offset + w_k)
 // ---------------------------------------------------------------------------------------------------------------------------------
 template <typename ST>
-__global__ void rms_norm2_kernel(ST* __restrict__ out1, ST* __restrict__ out2, const float* __restrict__ x, const float* __restrict__ w1,
-                                 const float* __restrict__ w2, float offset, float eps, int W) {
+__global__ void rms_norm2_kernel(ST* __restrict__ out1, ST* __restrict__ out2, float* __restrict__ x, const ST* __restrict__ add,
+                                 const float* __restrict__ w1, const float* __restrict__ w2, float offset, float eps, int W) {
   __shared__ float red[33];
-  const float* row = x + (size_t)blockIdx.x * W;
+  float* row = x + (size_t)blockIdx.x * W;
   float ss = 0.f;
   for (int i = threadIdx.x; i < W; i += blockDim.x) {
-    const float v = row[i];
+    float v = row[i];
+    if (add != nullptr) {  // the previous layer's update lands in the stream here: one pass instead of two
+      v += ldf(add + (size_t)blockIdx.x * W + i);
+      row[i] = v;
+    }
     ss += v * v;
   }
   ss = block_sum(ss, red);
   const float r = 1.f / sqrtf(ss / (float)W + eps);
   for (int i = threadIdx.x; i < W; i += blockDim.x) {
-    const float v = row[i] * r;
+    const float v = row[i] * r;  // each thread re-reads what it wrote itself
     stf(out1 + (size_t)blockIdx.x * W + i, v * (offset + w1[i]));
     if (out2 != nullptr) stf(out2 + (size_t)blockIdx.x * W + i, v * (offset + w2[i]));
   }
@@ -970,15 +974,16 @@ int qs_hyb_embed(float* out, const int32_t* tokens, const int32_t* prev, const v
   return check_cuda(cudaGetLastError(), "hyb_embed");
 }
 
-int qs_hyb_rms_norm(void* out1, void* out2, const float* x, const float* w1, const float* w2, float offset, float eps, int tokens_n, int width,
-                    int dtype, void* stream) {
+int qs_hyb_rms_norm(void* out1, void* out2, float* x, const void* add, const float* w1, const float* w2, float offset, float eps, int tokens_n,
+                    int width, int dtype, void* stream) {
   QS_REQUIRE(out1 && x && w1 && (out2 == nullptr || w2 != nullptr), "hyb_rms_norm: null tensor");
   if (tokens_n == 0) return qs::QS_OK;
   cudaStream_t s = (cudaStream_t)stream;
   const int threads = width >= 1024 ? 256 : 128;
   QS_DT(dtype,
-        (rms_norm2_kernel<__nv_bfloat16><<<tokens_n, threads, 0, s>>>((__nv_bfloat16*)out1, (__nv_bfloat16*)out2, x, w1, w2, offset, eps, width)),
-        (rms_norm2_kernel<float><<<tokens_n, threads, 0, s>>>((float*)out1, (float*)out2, x, w1, w2, offset, eps, width)));
+        (rms_norm2_kernel<__nv_bfloat16><<<tokens_n, threads, 0, s>>>((__nv_bfloat16*)out1, (__nv_bfloat16*)out2, x, (const __nv_bfloat16*)add, w1, w2,
+                                                                       offset, eps, width)),
+        (rms_norm2_kernel<float><<<tokens_n, threads, 0, s>>>((float*)out1, (float*)out2, x, (const float*)add, w1, w2, offset, eps, width)));
   return check_cuda(cudaGetLastError(), "hyb_rms_norm");
 }
 

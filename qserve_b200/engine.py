@@ -117,8 +117,12 @@ class Scheduler:
 
 class Engine:
     def __init__(self, model: HybridDecoder, max_tokens: int = 4096, max_seqs: int = 4, page_size: int = 64, max_batch_tokens: int = 2048,
-                 chunk: int = 512, seed: int = 0):
+                 chunk: int = 512, seed: int = 0, use_graphs: bool = True):
         self.model = model
+        # steps that only decode (one token per sequence, none at its first position) replay a CUDA graph captured per batch size: the
+        # launches of a step cost more host time than its kernels take
+        self.use_graphs = use_graphs
+        self._graphs: Dict[int, dict] = {}
         self.cache = model.new_cache(max_tokens, max_seqs, page_size)
         self.scheduler = Scheduler(self.cache, max_batch_tokens, chunk)
         self.generator = torch.Generator(device=model.device)
@@ -145,8 +149,13 @@ class Engine:
             rows.append((st.slot, st.length, st.last_token, list(toks)))
             want_rows += [r + int(w) for w in want]
             r += len(toks)
-        batch = StepBatch.build(rows, cache.sync_block_table(), self.model.device)
-        x = self.model.forward(batch, cache, tap)
+        table = cache.sync_block_table()
+        graphed = self.use_graphs and tap is None and all(len(r[3]) == 1 and r[1] > 0 for r in rows)
+        if graphed:
+            all_logits = self._decode_step(rows, table)
+            graphed = all_logits is not None
+        if not graphed:
+            x = self.model.forward(StepBatch.build(rows, table, self.model.device), cache, tap)
         for sid, toks, _ in entries:
             st = cache.seqs[sid]
             st.length += len(toks)
@@ -155,7 +164,40 @@ class Engine:
         if not want_rows:
             return torch.empty((0, self.model.cfg.vocab), dtype=torch.float32, device=self.model.device)
         idx = torch.tensor(want_rows, dtype=torch.int64, device=self.model.device)
+        if graphed:
+            return all_logits.index_select(0, idx)
         return self.model.logits(x.index_select(0, idx))
+
+    def _decode_step(self, rows, table) -> Optional[torch.Tensor]:
+        """Replay (capture at first use) the graph of a decode-only step of len(rows) sequences; returns the logits of all rows, or None if
+        capture failed (the step then runs eagerly and graphs stay off)."""
+        n, dev = len(rows), self.model.device
+        host, sizes = StepBatch.pack(rows)
+        g = self._graphs.get(n)
+        if g is None:
+            g = {"host": torch.empty_like(host).pin_memory(), "dev": torch.empty(host.numel(), dtype=torch.int32, device=dev), "sizes": sizes,
+                 "scratch": torch.empty(max(1, self.model.scratch_floats(n)), dtype=torch.float32, device=dev)}
+            g["batch"] = StepBatch.view(g["dev"], sizes, table)
+            g["host"].copy_(host)
+            g["dev"].copy_(g["host"], non_blocking=True)
+            graph = torch.cuda.CUDAGraph()
+            try:
+                torch.cuda.synchronize(dev)
+                with torch.cuda.graph(graph):
+                    g["logits"] = self.model.logits(self.model.forward(g["batch"], self.cache, None, g["scratch"]))
+            except RuntimeError as e:
+                print(f"[qserve_b200] CUDA-graph capture of the decode step failed, running eagerly: {e}", file=sys.stderr)
+                self.use_graphs = False
+                return None
+            g["graph"] = graph
+            self._graphs[n] = g
+        else:
+            assert g["sizes"] == sizes
+            torch.cuda.current_stream(dev).synchronize()  # the previous replay has consumed the pinned staging copy
+            g["host"].copy_(host)
+            g["dev"].copy_(g["host"], non_blocking=True)
+        g["graph"].replay()
+        return g["logits"]
 
     def release(self, seq_id) -> None:
         self.cache.release(seq_id)

@@ -60,8 +60,9 @@ class StepBatch:
     TILE_ROWS = 64
 
     @staticmethod
-    def build(entries: Sequence[tuple], block_table: torch.Tensor, device: torch.device) -> "StepBatch":
-        """entries: (slot, first position, previous token or -1, token list) per sequence, in batch order."""
+    def pack(entries: Sequence[tuple]):
+        """Host side of a batch: one int32 tensor holding every table, and the sizes (T, E, tiles, long rows, short rows) that say where.
+        entries: (slot, first position, previous token or -1, token list) per sequence, in batch order."""
         T = sum(len(e[3]) for e in entries)
         E = len(entries)
         tiles = [(i, r0) for i, e in enumerate(entries) if len(e[3]) >= StepBatch.TILE_MIN for r0 in range(0, len(e[3]), StepBatch.TILE_ROWS)]
@@ -87,13 +88,22 @@ class StepBatch:
         lists[:] = torch.tensor(longs + shorts, dtype=torch.int32)
         if nt:
             host[6 * T + 4 * E:] = torch.tensor([t[0] for t in tiles] + [t[1] for t in tiles], dtype=torch.int32)
-        if device.type == "cuda":
-            host = host.pin_memory()
-        d = host.to(device, non_blocking=True)
+        return host, (T, E, nt, len(longs), len(shorts))
+
+    @staticmethod
+    def view(d: torch.Tensor, sizes: tuple, block_table: torch.Tensor) -> "StepBatch":
+        """The batch over a device copy `d` of a packed host tensor."""
+        T, E, nt, n_long, n_short = sizes
         v = [d[i * T:(i + 1) * T] for i in range(5)] + [d[6 * T + i * E: 6 * T + (i + 1) * E] for i in range(4)]
         o = 6 * T + 4 * E
-        return StepBatch(T, E, *v, block_table, nt, len(longs), len(shorts), d[o:o + nt], d[o + nt:o + 2 * nt], d[5 * T:5 * T + len(longs)],
-                         d[5 * T + len(longs):6 * T])
+        return StepBatch(T, E, *v, block_table, nt, n_long, n_short, d[o:o + nt], d[o + nt:o + 2 * nt], d[5 * T:5 * T + n_long], d[5 * T + n_long:6 * T])
+
+    @staticmethod
+    def build(entries: Sequence[tuple], block_table: torch.Tensor, device: torch.device) -> "StepBatch":
+        host, sizes = StepBatch.pack(entries)
+        if device.type == "cuda":
+            host = host.pin_memory()
+        return StepBatch.view(host.to(device, non_blocking=True), sizes, block_table)
 
 
 # ------------------------------------------------------------------------------------------------------------------------
@@ -248,32 +258,42 @@ class HybridDecoder:
         return HybridCache(self.cfg, self.dtype, self.device, max_tokens, max_seqs, page_size)
 
     # ----------------------------------------------------------------------------------------------------------------
-    def forward(self, b: StepBatch, cache: HybridCache, tap=None) -> torch.Tensor:
-        """Residual stream [T, W] fp32 after the last layer run.  `tap(run_index, x)` (debugging / tests) sees it after every run."""
+    def scratch_floats(self, tokens: int) -> int:
+        return max((ly.mixer.scratch_floats(tokens) for ly in self.layers), default=0)
+
+    def forward(self, b: StepBatch, cache: HybridCache, tap=None, scratch: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Residual stream [T, W] fp32 after the last layer run.  `tap(run_index, x)` (debugging / tests) sees it after every run.
+        `scratch` (fp32, at least scratch_floats(T)): the caller's own work space, e.g. one that a captured CUDA graph keeps."""
         cfg, dev, dt, T, W = self.cfg, self.device, self.dt, b.n_tokens, self.cfg.width
         s = _stream(dev)
         x = torch.empty((T, W), dtype=torch.float32, device=dev)
         check(lib.qs_hyb_embed(x.data_ptr(), _p(b.tokens), _p(b.prev), self.embed.data_ptr(), _p(self.pair), T, W, cfg.pair_buckets,
                                cfg.pair_mul_prev, cfg.pair_mul_cur, dt, s))
-        need = max((ly.mixer.scratch_floats(T) for ly in self.layers), default=0)
-        if need and (self._scratch is None or self._scratch.numel() < need):
-            self._scratch = torch.empty(need, dtype=torch.float32, device=dev)
+        if scratch is None:
+            need = self.scratch_floats(T)
+            if need and (self._scratch is None or self._scratch.numel() < need):
+                self._scratch = torch.empty(need, dtype=torch.float32, device=dev)
+            scratch = self._scratch
         h1 = torch.empty((T, W), dtype=self.dtype, device=dev)
         h2 = torch.empty((T, W), dtype=self.dtype, device=dev)
+        upd = None  # the previous layer's update, still to be added to the stream
         for run, li in enumerate(self.schedule):
             ly = self.layers[li]
-            check(lib.qs_hyb_rms_norm(h1.data_ptr(), _p(h2) if ly.ff else None, x.data_ptr(), ly.norm1.data_ptr(), _p(ly.norm2), cfg.norm_offset,
-                                      cfg.eps, T, W, dt, s))
+            # the stream takes the previous layer's update inside this layer's norm kernel (one pass over x instead of two)
+            check(lib.qs_hyb_rms_norm(h1.data_ptr(), _p(h2) if ly.ff else None, x.data_ptr(), _p(upd) if tap is None else None, ly.norm1.data_ptr(),
+                                      _p(ly.norm2), cfg.norm_offset, cfg.eps, T, W, dt, s))
             proj = torch.mm(h1, ly.mixer.w_in.t())
             cat = torch.empty((T, ly.mixer.out_features + ly.ff), dtype=self.dtype, device=dev)
-            ly.mixer.run(proj, cat, b, cache.runs[run], cache.page_size, self._scratch, dt, s)
+            ly.mixer.run(proj, cat, b, cache.runs[run], cache.page_size, scratch, dt, s)
             if ly.ff:
                 gu = torch.mm(h2, ly.w_mlp_in.t())
                 check(lib.qs_hyb_gelu_tanh_mul(cat.data_ptr() + ly.mixer.out_features * cat.element_size(), cat.stride(0), gu.data_ptr(), T, ly.ff, dt, s))
             upd = torch.mm(cat, ly.w_out.t())
-            check(lib.qs_hyb_residual_add(x.data_ptr(), upd.data_ptr(), T * W, dt, s))
-            if tap is not None:
+            if tap is not None:  # observers want the stream after every run: add right away
+                check(lib.qs_hyb_residual_add(x.data_ptr(), upd.data_ptr(), T * W, dt, s))
                 tap(run, x)
+        if upd is not None and tap is None:
+            check(lib.qs_hyb_residual_add(x.data_ptr(), upd.data_ptr(), T * W, dt, s))
         return x
 
     def logits(self, x_rows: torch.Tensor) -> torch.Tensor:
@@ -281,7 +301,7 @@ class HybridDecoder:
         n, W = x_rows.shape
         x_rows = x_rows.contiguous()
         h = torch.empty((n, W), dtype=self.dtype, device=self.device)
-        check(lib.qs_hyb_rms_norm(h.data_ptr(), None, x_rows.data_ptr(), self.final_norm.data_ptr(), None, self.cfg.norm_offset, self.cfg.eps, n, W,
+        check(lib.qs_hyb_rms_norm(h.data_ptr(), None, x_rows.data_ptr(), None, self.final_norm.data_ptr(), None, self.cfg.norm_offset, self.cfg.eps, n, W,
                                   self.dt, _stream(self.device)))
         return torch.mm(h, self.head.t()).float()
 

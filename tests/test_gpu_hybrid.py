@@ -163,6 +163,33 @@ def test_unequal_requests_in_one_batch_and_reused_pages_and_slots(dev):
         assert row_err(torch.cat(got[k]), want[k]) < F32_TOL, k
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_graph_replay_equals_eager_launches(dev, dtype):
+    """Decode-only steps replay a CUDA graph captured per batch size; the logits are those of eager launches up to rounding (the vendor
+    matrix products may pick another algorithm inside a capture), also when the batch size changes, a sequence ends and its slot and pages
+    go to a new one."""
+    cfg = make_config(MIXED, loop=(1, 3, 2))
+    w = make_weights(cfg, 13)
+    reqs = [random_tokens(n, cfg["vocab"], 30 + i) for i, n in enumerate([40, 90, 23, 70])]
+    outs = []
+    for graphs in (True, False):
+        eng = _engine(cfg, w, dtype, max_tokens=5 * 64, max_seqs=3, use_graphs=graphs)
+        got = []
+        eng.step([(i, reqs[i][:20], []) for i in range(3)])
+        for t in range(20, 23):
+            got.append(eng.step([(i, reqs[i][t:t + 1], [0]) for i in range(3)]))
+        eng.release(2)
+        eng.step([(3, reqs[3][:50], [])])
+        for t in range(23, 40):
+            got.append(eng.step([(0, reqs[0][t:t + 1], [0]), (1, reqs[1][t:t + 1], [0]), (3, reqs[3][t + 27:t + 28], [0])]))
+        eng.release(0)
+        for t in range(40, 43):
+            got.append(eng.step([(1, reqs[1][t:t + 1], []), (3, reqs[3][t + 27:t + 28], [0])]))
+        assert bool(eng._graphs) == graphs
+        outs.append(torch.cat(got))
+    assert row_err(outs[0], outs[1]) < (1e-5 if dtype == torch.float32 else 2e-2)
+
+
 def test_long_decoding(dev):
     cfg = make_config([delta_layer(conv=3), attention_layer()], loop=(0, 2, 2))
     w = make_weights(cfg, 8)
