@@ -699,9 +699,12 @@ def hybrid_block(args):
             kern["delta_prefill(conv+scan+gate)"] = {"us": td * 1e6, "tokens_per_s": T / td}
             x = torch.randn(T, W, device=dev)
             h1, h2 = torch.empty(T, W, dtype=torch.bfloat16, device=dev), torch.empty(T, W, dtype=torch.bfloat16, device=dev)
-            tn = time_kernel(lambda: (check(lib.qs_hyb_rms_norm(h1.data_ptr(), h2.data_ptr(), x.data_ptr(), None, ly_a.norm1.data_ptr(), ly_a.norm2.data_ptr(),
-                                                                 1.0, 1e-5, T, W, 0, raw())), 1)[1], reps, stream)
-            kern["rms_norm_dual"] = {"us": tn * 1e6, "frac_of_measured_hbm": T * W * 8 / tn / 1e9 / hbm_gbs}
+            upd = torch.zeros(T, W, dtype=torch.bfloat16, device=dev)
+            # as the engine runs it: the stream takes the previous layer's update (bf16 in, fp32 in and out) and leaves two normalised bf16 rows
+            tn = time_kernel(lambda: (check(lib.qs_hyb_rms_norm(h1.data_ptr(), h2.data_ptr(), x.data_ptr(), upd.data_ptr(), ly_a.norm1.data_ptr(),
+                                                                 ly_a.norm2.data_ptr(), 1.0, 1e-5, T, W, 0, raw())), 1)[1], reps, stream)
+            kern["add_rms_norm_dual"] = {"us": tn * 1e6, "frac_of_measured_hbm": T * W * 14 / tn / 1e9 / hbm_gbs}
+            del upd
             gu = torch.randn(T, 2 * FF, device=dev).to(torch.bfloat16)
             tg = time_kernel(lambda: (check(lib.qs_hyb_gelu_tanh_mul(cat.data_ptr(), cat.stride(0), gu.data_ptr(), T, FF, 0, raw())), 1)[1], reps, stream)
             kern["gelu_tanh_mul"] = {"us": tg * 1e6, "frac_of_measured_hbm": T * FF * 6 / tg / 1e9 / hbm_gbs}
@@ -733,6 +736,18 @@ def hybrid_block(args):
             run.qkv_buf.normal_()
             ta = time_kernel(lambda: (run._attention(0), 1)[1], reps * 4, stream)
             peer["attention_decode_kv4"] = {"us": ta * 1e6, "frac_of_measured_hbm": run.kv_bytes_per_step() / run.L / ta / 1e9 / hbm_gbs}
+            T = NP * LP
+            xh, dl = torch.randn(T, W, device=dev).half(), torch.randn(T, W, device=dev).half()
+            qo, ho = torch.empty(T, W, dtype=torch.int8, device=dev), torch.empty(T, W, dtype=torch.float16, device=dev)
+            qs_, sc = torch.empty(T, dtype=torch.float16, device=dev), torch.empty(T, dtype=torch.float16, device=dev)
+            gam = torch.ones(W, dtype=torch.float16, device=dev)
+            tn = time_kernel(lambda: (backend.add_rms_norm_general(qo, ho, xh, dl, gam, qs_, sc, 1e-5), 1)[1], reps, stream)
+            peer["add_rms_norm_quant"] = {"us": tn * 1e6, "frac_of_measured_hbm": T * W * 7 / tn / 1e9 / hbm_gbs}
+            guh = torch.randn(T, 2 * FF, device=dev).half()
+            qm = torch.empty(T, FF, dtype=torch.int8, device=dev)
+            tg = time_kernel(lambda: (backend.silu_and_mul_quant(qm, guh, qs_, sc), 1)[1], reps, stream)
+            peer["silu_and_mul_quant"] = {"us": tg * 1e6, "frac_of_measured_hbm": T * FF * 5 / tg / 1e9 / hbm_gbs}
+            del xh, dl, qo, ho, guh, qm
             q = torch.randn(NP * LP, H, D, device=dev).half()
             k = torch.randn(NP * LP, G, D, device=dev).half()
             cu = torch.arange(0, NP * LP + 1, LP, dtype=torch.int32, device=dev)

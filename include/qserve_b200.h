@@ -236,9 +236,12 @@ QS_API int qs_hyb_attention(void* out, int64_t out_stride, const void* q, int64_
                             int head_norm, int page_size, int dtype, void* stream);
 /* The same attention on the fast kernels (bfloat16 storage, dim and vdim multiples of 16, vdim in {32, 64, 96, 128, 256}, heads / kv_heads <= 16):
  * entries of at least 16 tokens run as 64-row tiles on the tensor cores (tile_entry / tile_row0: entry and first row within it of every tile;
- * long_tokens: their token rows; scratch fp32 [tokens, heads, maps, vdim]), the tokens listed in short_tokens on the vectorised single-token
- * kernel.  qs_hyb_attention_fast_supported returns 1 if the shape qualifies. */
+ * long_tokens: their token rows), the tokens listed in short_tokens one by one, the query heads of a key/value head as the rows of a
+ * tensor-core tile and the keys shared out over several blocks.  scratch: fp32, qs_hyb_attention_scratch_floats elements.
+ * qs_hyb_attention_fast_supported returns 1 if the shape qualifies. */
 QS_API int qs_hyb_attention_fast_supported(int dtype, int heads, int kv_heads, int maps, int dim, int vdim, int64_t q_stride);
+/* fp32 elements of scratch that qs_hyb_attention_fast needs for a step of `tokens` tokens */
+QS_API int64_t qs_hyb_attention_scratch_floats(int tokens, int heads, int kv_heads, int maps, int vdim);
 QS_API int qs_hyb_attention_fast(void* out, int64_t out_stride, const void* q, int64_t q_stride, const void* kpool, const void* vpool,
                                  const int32_t* tok_slot, const int32_t* tok_pos, const int32_t* block_table, int max_blocks,
                                  const int32_t* tile_entry, const int32_t* tile_row0, int n_tiles, const int32_t* long_tokens, int n_long,

@@ -58,6 +58,7 @@ SIGNATURES = {
     "qs_hyb_rope_append": (c_int, [_P, _L, _P, _P, _P, _I, _P, _P, _P, _F, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P]),
     "qs_hyb_attention": (c_int, [_P, _L, _P, _L, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _F, _F, _F, _I, _I, _I, _P]),
     "qs_hyb_attention_fast_supported": (c_int, [_I, _I, _I, _I, _I, _I, _L]),
+    "qs_hyb_attention_scratch_floats": (_L, [_I, _I, _I, _I, _I]),
     "qs_hyb_attention_fast": (c_int, [_P, _L, _P, _L, _P, _P, _P, _P, _P, _I, _P, _P, _I, _P, _I, _P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I,
                                       _F, _F, _F, _F, _I, _I, _I, _P]),
     "qs_hyb_gated_delta": (c_int, [_P, _L, _P, _P, _P, _L, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _F, _I, _P]),

@@ -104,6 +104,49 @@ __global__ void rms_norm2_kernel(ST* __restrict__ out1, ST* __restrict__ out2, f
   }
 }
 
+// four elements of the storage type at once
+template <typename ST> __device__ __forceinline__ float4 ld4(const ST* p);
+template <> __device__ __forceinline__ float4 ld4<float>(const float* p) { return *reinterpret_cast<const float4*>(p); }
+template <> __device__ __forceinline__ float4 ld4<__nv_bfloat16>(const __nv_bfloat16* p) {
+  const uint2 u = *reinterpret_cast<const uint2*>(p);
+  return make_float4(__uint_as_float(u.x << 16), __uint_as_float(u.x & 0xffff0000u), __uint_as_float(u.y << 16), __uint_as_float(u.y & 0xffff0000u));
+}
+template <typename ST> __device__ __forceinline__ void st4(ST* p, float4 v);
+template <> __device__ __forceinline__ void st4<float>(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+template <> __device__ __forceinline__ void st4<__nv_bfloat16>(__nv_bfloat16* p, float4 v) {
+  __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+  *reinterpret_cast<uint2*>(p) = make_uint2(*reinterpret_cast<uint32_t*>(&a), *reinterpret_cast<uint32_t*>(&b));
+}
+
+// the same norm for widths that are multiples of 4: 16-byte accesses to the stream and the gains, 8- or 16-byte ones to the outputs
+template <typename ST>
+__global__ void rms_norm2_vec_kernel(ST* __restrict__ out1, ST* __restrict__ out2, float* __restrict__ x, const ST* __restrict__ add,
+                                     const float* __restrict__ w1, const float* __restrict__ w2, float offset, float eps, int W) {
+  __shared__ float red[33];
+  const size_t base = (size_t)blockIdx.x * W;
+  float ss = 0.f;
+  for (int i = threadIdx.x * 4; i < W; i += blockDim.x * 4) {
+    float4 v = ld4(x + base + i);
+    if (add != nullptr) {
+      const float4 a = ld4(add + base + i);
+      v.x += a.x; v.y += a.y; v.z += a.z; v.w += a.w;
+      st4(x + base + i, v);
+    }
+    ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+  }
+  ss = block_sum(ss, red);
+  const float r = 1.f / sqrtf(ss / (float)W + eps);
+  for (int i = threadIdx.x * 4; i < W; i += blockDim.x * 4) {
+    const float4 v = ld4(x + base + i);  // each thread re-reads what it wrote itself
+    const float4 g = ld4(w1 + i);
+    st4(out1 + base + i, make_float4(v.x * r * (offset + g.x), v.y * r * (offset + g.y), v.z * r * (offset + g.z), v.w * r * (offset + g.w)));
+    if (out2 != nullptr) {
+      const float4 h = ld4(w2 + i);
+      st4(out2 + base + i, make_float4(v.x * r * (offset + h.x), v.y * r * (offset + h.y), v.z * r * (offset + h.z), v.w * r * (offset + h.w)));
+    }
+  }
+}
+
 // x += y  (fp32 stream, y in the storage type)
 template <typename ST>
 __global__ void residual_add_kernel(float* __restrict__ x, const ST* __restrict__ y, size_t n) {
@@ -120,6 +163,24 @@ __global__ void gelu_tanh_mul_kernel(ST* __restrict__ out, long long out_stride,
   const float z = ldf(in + (size_t)t * 2 * ff + i), u = ldf(in + (size_t)t * 2 * ff + ff + i);
   const float g = 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
   stf(out + (size_t)t * out_stride + i, g * u);
+}
+
+// bfloat16 rows, eight elements per thread.  0.5 (1 + tanh u) = 1 / (1 + e^(-2u)): one exponential and one division on the special-function
+// unit, relative error near 2^-21, far below the rounding of the bfloat16 result (the fp32 kernel above keeps tanhf)
+__global__ void gelu_tanh_mul_bf16x8_kernel(__nv_bfloat16* __restrict__ out, long long out_stride, const __nv_bfloat16* __restrict__ in, int ff) {
+  const int t = blockIdx.x;
+  const int i = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
+  if (i >= ff) return;
+  const __nv_bfloat16* row = in + (size_t)t * 2 * ff;
+  const float4 z0 = ld4(row + i), z1 = ld4(row + i + 4), u0 = ld4(row + ff + i), u1 = ld4(row + ff + i + 4);
+  auto f = [](float z, float u) {
+    const float a = 0.7978845608028654f * (z + 0.044715f * z * z * z);
+    float e;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(-2.f * 1.4426950408889634f * a));
+    return __fdividef(z, 1.f + e) * u;
+  };
+  st4(out + (size_t)t * out_stride + i, make_float4(f(z0.x, u0.x), f(z0.y, u0.y), f(z0.z, u0.z), f(z0.w, u0.w)));
+  st4(out + (size_t)t * out_stride + i + 4, make_float4(f(z1.x, u1.x), f(z1.y, u1.y), f(z1.z, u1.z), f(z1.w, u1.w)));
 }
 
 // ---------------------------------------------------------------------------------------------------------------------------------
@@ -317,11 +378,25 @@ __device__ __forceinline__ void ldsm_x4_trans(uint32_t (&r)[4], const void* p) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
 }
 __device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+  asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 __device__ __forceinline__ void cp_async16(void* dst, const void* src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
+}
+// 2^x on the special-function unit (relative error about 2^-22; -inf gives 0): the bfloat16 kernels' softmax runs in the base-2 domain
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+// the leading bfloat16 terms of two fp32 numbers, packed; the numbers keep what is left
+__device__ __forceinline__ uint32_t split_bf16x2(float& lo, float& hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  const uint32_t u = *reinterpret_cast<uint32_t*>(&v);
+  lo -= __uint_as_float(u << 16);
+  hi -= __uint_as_float(u & 0xffff0000u);
+  return u;
 }
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
@@ -359,20 +434,25 @@ __global__ void __launch_bounds__(128) tile_attention_kernel(
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
   const int last_qpos = qpos0 + n_rows - 1;
   const int n_kt = last_qpos / kTileK + 1;
+  const float scale_log2 = scale * 1.4426950408889634f;
   const int qrow = warp * 16 + (lane >> 2);  // this thread's rows: qrow, qrow + 8
   // key / value tiles are double-buffered: tile kt + 1 streams in with cp.async while tile kt is multiplied
+  // two threads per key row, alternating 16-byte chunks: one block-table lookup per thread and tile
   auto load_kv = [&](int kt, int buf) {
-    __nv_bfloat16* Kd = Ks + (size_t)buf * kTileK * SD;
-    __nv_bfloat16* Vd = Vs + (size_t)buf * kTileK * SV;
-    for (int c = tid; c < kTileK * dch; c += 128) {
-      const int r = c / dch, cc = c - r * dch, kp = kt * kTileK + r;
-      if (kp <= last_qpos) cp_async16(Kd + r * SD + cc * 8, kpool + ((((size_t)bt[kp / page] * page + kp % page) * G + g) * maps + m) * (size_t)D + cc * 8);
-      else *reinterpret_cast<uint4*>(Kd + r * SD + cc * 8) = make_uint4(0, 0, 0, 0);
-    }
-    for (int c = tid; c < kTileK * (Dv / 8); c += 128) {
-      const int r = c / (Dv / 8), cc = c - r * (Dv / 8), kp = kt * kTileK + r;
-      if (kp <= last_qpos) cp_async16(Vd + r * SV + cc * 8, vpool + (((size_t)bt[kp / page] * page + kp % page) * G + g) * (size_t)Dv + cc * 8);
-      else *reinterpret_cast<uint4*>(Vd + r * SV + cc * 8) = make_uint4(0, 0, 0, 0);
+    const int r = tid >> 1, kp = kt * kTileK + r;
+    __nv_bfloat16* Kd = Ks + (size_t)buf * kTileK * SD + r * SD;
+    __nv_bfloat16* Vd = Vs + (size_t)buf * kTileK * SV + r * SV;
+    if (kp <= last_qpos) {
+      const size_t cell = (size_t)bt[kp / page] * page + kp % page;
+      const __nv_bfloat16* ksrc = kpool + ((cell * G + g) * maps + m) * (size_t)D;
+      const __nv_bfloat16* vsrc = vpool + (cell * G + g) * (size_t)Dv;
+      for (int cc = tid & 1; cc < dch; cc += 2) cp_async16(Kd + cc * 8, ksrc + cc * 8);
+#pragma unroll
+      for (int cc = tid & 1; cc < Dv / 8; cc += 2) cp_async16(Vd + cc * 8, vsrc + cc * 8);
+    } else {
+      for (int cc = tid & 1; cc < dch; cc += 2) *reinterpret_cast<uint4*>(Kd + cc * 8) = make_uint4(0, 0, 0, 0);
+#pragma unroll
+      for (int cc = tid & 1; cc < Dv / 8; cc += 2) *reinterpret_cast<uint4*>(Vd + cc * 8) = make_uint4(0, 0, 0, 0);
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
   };
@@ -403,13 +483,17 @@ __global__ void __launch_bounds__(128) tile_attention_kernel(
     }
     // scale, causal mask, online softmax (rows qrow and qrow + 8; a row's 64 columns live in the 4 lanes of a quad)
     float mx[2] = {-INFINITY, -INFINITY};
+    const bool diagonal = kt * kTileK + kTileK - 1 > qpos0 + warp * 16;
 #pragma unroll
     for (int nt = 0; nt < 8; ++nt)
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        const int kpos = kt * kTileK + nt * 8 + (lane & 3) * 2 + (j & 1);
-        const int qp = qpos0 + qrow + (j >> 1) * 8;
-        const float v = kpos <= qp ? s[nt][j] * scale : -INFINITY;
+        float v = s[nt][j] * scale_log2;
+        if (diagonal) {  // warp-uniform: only tiles that reach past this warp's first row need the causal mask
+          const int kpos = kt * kTileK + nt * 8 + (lane & 3) * 2 + (j & 1);
+          const int qp = qpos0 + qrow + (j >> 1) * 8;
+          if (kpos > qp) v = -INFINITY;
+        }
         s[nt][j] = v;
         mx[j >> 1] = fmaxf(mx[j >> 1], v);
       }
@@ -419,7 +503,7 @@ __global__ void __launch_bounds__(128) tile_attention_kernel(
       mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
       mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
       const float m_new = fmaxf(m_run[r], mx[r]);
-      corr[r] = m_new == -INFINITY ? 1.f : expf(m_run[r] - m_new);
+      corr[r] = m_new == -INFINITY ? 1.f : fast_exp2(m_run[r] - m_new);
       m_run[r] = m_new;
       l_run[r] *= corr[r];
     }
@@ -428,7 +512,7 @@ __global__ void __launch_bounds__(128) tile_attention_kernel(
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         const float mm = m_run[j >> 1];
-        const float p = mm == -INFINITY ? 0.f : expf(s[nt][j] - mm);
+        const float p = mm == -INFINITY ? 0.f : fast_exp2(s[nt][j] - mm);
         s[nt][j] = p;
         l_run[j >> 1] += p;
       }
@@ -436,6 +520,9 @@ __global__ void __launch_bounds__(128) tile_attention_kernel(
     for (int i = 0; i < 2 * NVT; ++i) {
       o[i][0] *= corr[0]; o[i][1] *= corr[0]; o[i][2] *= corr[1]; o[i][3] *= corr[1];
     }
+    // P V: value fragments of NVG column blocks are held while the PSPLIT terms of the weights pass, so that two products into the same
+    // accumulator are 2 NVG instructions apart
+    constexpr int NVG = NVT % 4 == 0 ? 4 : 2;
 #pragma unroll
     for (int kk = 0; kk < 4; ++kk) {  // 16 keys per step
       uint32_t a[PSPLIT][4];
@@ -444,24 +531,21 @@ __global__ void __launch_bounds__(128) tile_attention_kernel(
         const int nt = 2 * kk + (part >> 1), j0 = (part & 1) * 2;
         float r0v = s[nt][j0], r1v = s[nt][j0 + 1];
 #pragma unroll
-        for (int sp = 0; sp < PSPLIT; ++sp) {
-          const __nv_bfloat16 h0 = __float2bfloat16_rn(r0v), h1 = __float2bfloat16_rn(r1v);
-          __nv_bfloat162 pr;
-          pr.x = h0; pr.y = h1;
-          a[sp][part] = *reinterpret_cast<uint32_t*>(&pr);
-          r0v -= __bfloat162float(h0);
-          r1v -= __bfloat162float(h1);
-        }
+        for (int sp = 0; sp < PSPLIT; ++sp) a[sp][part] = split_bf16x2(r0v, r1v);
       }
 #pragma unroll
-      for (int nv = 0; nv < NVT; ++nv) {
-        uint32_t b[4];
-        ldsm_x4_trans(b, Vc + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * SV + nv * 16 + (lane >> 4) * 8);
+      for (int nv0 = 0; nv0 < NVT; nv0 += NVG) {
+        uint32_t b[NVG][4];
 #pragma unroll
-        for (int sp = 0; sp < PSPLIT; ++sp) {
-          mma_bf16(o[2 * nv], a[sp], b[0], b[1]);
-          mma_bf16(o[2 * nv + 1], a[sp], b[2], b[3]);
-        }
+        for (int i = 0; i < NVG; ++i)
+          ldsm_x4_trans(b[i], Vc + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * SV + (nv0 + i) * 16 + (lane >> 4) * 8);
+#pragma unroll
+        for (int sp = 0; sp < PSPLIT; ++sp)
+#pragma unroll
+          for (int i = 0; i < NVG; ++i) {
+            mma_bf16(o[2 * (nv0 + i)], a[sp], b[i][0], b[i][1]);
+            mma_bf16(o[2 * (nv0 + i) + 1], a[sp], b[i][2], b[i][3]);
+          }
       }
     }
     __syncthreads();  // every warp is done with this buffer before tile kt + 2 streams into it
@@ -503,171 +587,225 @@ __global__ void multimap_combine_kernel(ST* __restrict__ out, long long out_stri
 }
 
 // ---------------------------------------------------------------------------------------------------------------------------------
-// Single tokens and short portions (bfloat16 storage, 16-byte loads).  One block per (listed token, kv head); warp w serves query head
-// g * R + w % R of the group (R = H / G) and, when a block has more warps than the group has heads, a share of the keys; the warps of a group
-// walk the same key / value rows at about the same time, so a row comes from HBM once.  A warp handles KPI keys per iteration: all 32 lanes
-// score each key (16-byte chunks of the [map 1 | map 2] row, warp-reduced per map), then LPK lanes per key accumulate the weighted value
-// chunk for every map.  Each warp keeps its own running maximum and sum; partials are merged through shared memory, then the head is
-// finished as in multimap_combine_kernel.
+// Single tokens on the tensor cores (bfloat16 storage).  The R = H / G query heads that share a key/value head are the rows of one m16n8k16
+// tile, so a key row is loaded once for the group and scored by the tensor cores instead of R warp reductions.  One block = (listed token,
+// kv head, map, share of the keys); its four warps each take 16 of the 64 keys of a tile that the block stages with cp.async (double
+// buffered), keep their own running maximum / sum / accumulators, and merge through shared memory at the end.  The block writes
+// [maximum (base-2 domain), sum, unnormalised output] per head to part[listed token][head][map][share]; group_merge_kernel merges the
+// shares, combines the maps and finishes the head.
 // ---------------------------------------------------------------------------------------------------------------------------------
-constexpr int kDecKeys = 4;   // keys a warp handles per iteration
-
-// QCH: 16-byte chunks of the [map 1 | map 2] key row per lane (maps * dim <= 256 QCH)
-template <int MAPS, int QCH>
-__global__ void __launch_bounds__(512) decode_vec_attention_kernel(__nv_bfloat16* __restrict__ out, long long out_stride, const __nv_bfloat16* __restrict__ q, long long q_stride,
-                                            const __nv_bfloat16* __restrict__ kpool, const __nv_bfloat16* __restrict__ vpool,
-                                            const int* __restrict__ tok_list, const int* __restrict__ tok_slot, const int* __restrict__ tok_pos,
-                                            const int* __restrict__ block_table, int max_blocks, int H, int G, int D, int Dv, int wph, float scale,
-                                            float lambda, float out_scale, float eps, int head_norm, int page) {
-  extern __shared__ float smf[];  // merge space [warps][MAPS][2 + Dv]
-  const int R = H / G;
-  const int t = tok_list[blockIdx.x], g = blockIdx.y;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int hl = warp % R, part = warp / R;  // head within the group, share of the keys
-  const int h = g * R + hl;
-  const int pos = tok_pos[t];
+template <int NVT, int PSPLIT>
+__global__ void __launch_bounds__(128) group_attention_kernel(
+    float* __restrict__ part, const __nv_bfloat16* __restrict__ q, long long q_stride, const __nv_bfloat16* __restrict__ kpool,
+    const __nv_bfloat16* __restrict__ vpool, const int* __restrict__ tok_list, const int* __restrict__ tok_slot, const int* __restrict__ tok_pos,
+    const int* __restrict__ block_table, int max_blocks, int H, int G, int maps, int D, float scale, int page, int shares) {
+  extern __shared__ __align__(16) unsigned char smraw[];
+  constexpr int Dv = NVT * 16;
+  const int SD = D + kPad, SV = Dv + kPad, R = H / G;
+  __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smraw);  // 16 rows, the group's heads first
+  __nv_bfloat16* Ks = Qs + 16 * SD;
+  __nv_bfloat16* Vs = Ks + 2 * kTileK * SD;
+  const int li = blockIdx.x, g = blockIdx.y / maps, m = blockIdx.y - g * maps, share = blockIdx.z;
+  const int t = tok_list[li], pos = tok_pos[t];
   const int* bt = block_table + (size_t)tok_slot[t] * max_blocks;
-  const int kch = (MAPS * D) >> 3, vch = Dv >> 3;
-  const int lpk = vch <= 16 ? 16 : 32, kpi = 32 / lpk;  // lanes per key in the value phase, keys per value pass
-  const int sub = lane / lpk, vc = lane % lpk;
-  // this lane's query chunks stay in registers, pre-multiplied by scale * log2(e): scores come out in the exp2 domain
-  float qr[QCH][8];
-  const float qscale = scale * 1.4426950408889634f;
-#pragma unroll
-  for (int i = 0; i < QCH; ++i) {
-    const int c = lane + 32 * i;
-#pragma unroll
-    for (int j = 0; j < 8; ++j) qr[i][j] = c < kch ? __bfloat162float(q[(size_t)t * q_stride + (size_t)h * MAPS * D + c * 8 + j]) * qscale : 0.f;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int dch = D >> 3;
+  const int n_kt = pos / kTileK + 1, per = (n_kt + shares - 1) / shares;
+  const int kt0 = share * per, kt1 = min(n_kt, kt0 + per);
+  float* pout = part + ((((size_t)li * H + g * R) * maps + m) * shares + share) * (size_t)(2 + Dv);  // head g R + r: + r maps shares (2 + Dv)
+  const size_t head_step = (size_t)maps * shares * (2 + Dv);
+  if (kt0 >= kt1) {  // a share without keys weighs nothing in the merge
+    for (int r = tid; r < R; r += 128) { pout[r * head_step] = -INFINITY; pout[r * head_step + 1] = 0.f; }
+    return;
   }
-  float m_run[MAPS], l_run[MAPS], acc[MAPS][8];
-#pragma unroll
-  for (int mm = 0; mm < MAPS; ++mm) {
-    m_run[mm] = -INFINITY; l_run[mm] = 0.f;
-#pragma unroll
-    for (int j = 0; j < 8; ++j) acc[mm][j] = 0.f;
+  for (int c = tid; c < 16 * dch; c += 128) {
+    const int r = c / dch, cc = c - r * dch;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (r < R) v = *reinterpret_cast<const uint4*>(q + (size_t)t * q_stride + (size_t)((g * R + r) * maps + m) * D + cc * 8);
+    *reinterpret_cast<uint4*>(Qs + r * SD + cc * 8) = v;
   }
-  const int n_keys = pos + 1;
-  for (int k0 = part * kDecKeys; k0 < n_keys; k0 += wph * kDecKeys) {
-    // all loads of the iteration first: the key chunks of four keys and this lane's value chunks
-    uint4 kv[kDecKeys][QCH], vv[kDecKeys];
+  float o[2 * NVT][4];
 #pragma unroll
-    for (int u = 0; u < kDecKeys; ++u) {
-      const int kj = min(k0 + u, n_keys - 1);  // clamped: a key beyond the end is loaded again and masked below
-      const size_t cell = (size_t)bt[kj / page] * page + kj % page;
-      const __nv_bfloat16* kr = kpool + (cell * G + g) * (size_t)(MAPS * D);
+  for (int i = 0; i < 2 * NVT; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+  const float scale_log2 = scale * 1.4426950408889634f;
+  // two threads per key row, alternating 16-byte chunks: one block-table lookup per thread and tile
+  auto load_kv = [&](int kt, int buf) {
+    const int r = tid >> 1, kp = kt * kTileK + r;
+    __nv_bfloat16* Kd = Ks + (size_t)buf * kTileK * SD + r * SD;
+    __nv_bfloat16* Vd = Vs + (size_t)buf * kTileK * SV + r * SV;
+    if (kp <= pos) {
+      const size_t cell = (size_t)bt[kp / page] * page + kp % page;
+      const __nv_bfloat16* ksrc = kpool + ((cell * G + g) * maps + m) * (size_t)D;
+      const __nv_bfloat16* vsrc = vpool + (cell * G + g) * (size_t)Dv;
+      for (int cc = tid & 1; cc < dch; cc += 2) cp_async16(Kd + cc * 8, ksrc + cc * 8);
 #pragma unroll
-      for (int i = 0; i < QCH; ++i)
-        if (lane + 32 * i < kch) kv[u][i] = *reinterpret_cast<const uint4*>(kr + (lane + 32 * i) * 8);
-      vv[u] = make_uint4(0, 0, 0, 0);
-      if ((u % kpi) == sub && vc < vch) vv[u] = *reinterpret_cast<const uint4*>(vpool + (cell * G + g) * (size_t)Dv + vc * 8);
+      for (int cc = tid & 1; cc < Dv / 8; cc += 2) cp_async16(Vd + cc * 8, vsrc + cc * 8);
+    } else {
+      for (int cc = tid & 1; cc < dch; cc += 2) *reinterpret_cast<uint4*>(Kd + cc * 8) = make_uint4(0, 0, 0, 0);
+#pragma unroll
+      for (int cc = tid & 1; cc < Dv / 8; cc += 2) *reinterpret_cast<uint4*>(Vd + cc * 8) = make_uint4(0, 0, 0, 0);
     }
-    float sc[kDecKeys][MAPS];
-#pragma unroll
-    for (int u = 0; u < kDecKeys; ++u) {
-      float d[MAPS];
-#pragma unroll
-      for (int mm = 0; mm < MAPS; ++mm) d[mm] = 0.f;
-#pragma unroll
-      for (int i = 0; i < QCH; ++i) {
-        const int c = lane + 32 * i;
-        if (c < kch) {
-          const __nv_bfloat162* k2 = reinterpret_cast<const __nv_bfloat162*>(&kv[u][i]);
-          float a = 0.f;
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const float2 f = __bfloat1622float2(k2[j]);
-            a += qr[i][2 * j] * f.x + qr[i][2 * j + 1] * f.y;
-          }
-          if (MAPS == 1 || c * 8 < D) d[0] += a; else d[MAPS - 1] += a;
-        }
-      }
-#pragma unroll
-      for (int mm = 0; mm < MAPS; ++mm) sc[u][mm] = k0 + u < n_keys ? warp_sum(d[mm]) : -INFINITY;
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  load_kv(kt0, 0);
+  for (int kt = kt0; kt < kt1; ++kt) {
+    const int buf = (kt - kt0) & 1;
+    if (kt + 1 < kt1) {
+      load_kv(kt + 1, buf ^ 1);
+      asm volatile("cp.async.wait_group 1;" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
     }
+    __syncthreads();
+    const __nv_bfloat16* Kc = Ks + (size_t)buf * kTileK * SD;
+    const __nv_bfloat16* Vc = Vs + (size_t)buf * kTileK * SV;
+    float s[2][4];  // this warp's 16 keys of the tile: two blocks of 8
 #pragma unroll
-    for (int mm = 0; mm < MAPS; ++mm) {
-      float mx = sc[0][mm];
-#pragma unroll
-      for (int u = 1; u < kDecKeys; ++u) mx = fmaxf(mx, sc[u][mm]);
-      if (mx > m_run[mm]) {  // warp-uniform: the running maximum moves, rescale what has been gathered
-        const float corr = exp2f(m_run[mm] - mx);
-        l_run[mm] *= corr;
-#pragma unroll
-        for (int j = 0; j < 8; ++j) acc[mm][j] *= corr;
-        m_run[mm] = mx;
-      }
-#pragma unroll
-      for (int u = 0; u < kDecKeys; ++u) {
-        const float p = exp2f(sc[u][mm] - m_run[mm]);
-        l_run[mm] += p;
-        sc[u][mm] = p;
-      }
+    for (int i = 0; i < 2; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+    for (int ks = 0; ks < D; ks += 16) {
+      uint32_t a[4], b[4];
+      ldsm_x4(a, Qs + ((lane & 7) + ((lane >> 3) & 1) * 8) * SD + ks + (lane >> 4) * 8);
+      ldsm_x4(b, Kc + (warp * 16 + (lane & 7) + (lane >> 4) * 8) * SD + ks + ((lane >> 3) & 1) * 8);
+      mma_bf16(s[0], a, b[0], b[1]);
+      mma_bf16(s[1], a, b[2], b[3]);
     }
+    float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-    for (int u = 0; u < kDecKeys; ++u) {
-      const __nv_bfloat162* v2 = reinterpret_cast<const __nv_bfloat162*>(&vv[u]);  // zeros where this lane does not serve key u
+    for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        const float2 f = __bfloat1622float2(v2[j]);
+        const int kpos = kt * kTileK + warp * 16 + nt * 8 + (lane & 3) * 2 + (j & 1);
+        const float v = kpos <= pos ? s[nt][j] * scale_log2 : -INFINITY;
+        s[nt][j] = v;
+        mx[j >> 1] = fmaxf(mx[j >> 1], v);
+      }
+    float corr[2];
 #pragma unroll
-        for (int mm = 0; mm < MAPS; ++mm) {
-          acc[mm][2 * j] += sc[u][mm] * f.x;
-          acc[mm][2 * j + 1] += sc[u][mm] * f.y;
+    for (int r = 0; r < 2; ++r) {
+      mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+      mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+      const float m_new = fmaxf(m_run[r], mx[r]);
+      corr[r] = m_new == -INFINITY ? 1.f : fast_exp2(m_run[r] - m_new);
+      m_run[r] = m_new;
+      l_run[r] *= corr[r];
+    }
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float mm = m_run[j >> 1];
+        const float p = mm == -INFINITY ? 0.f : fast_exp2(s[nt][j] - mm);
+        s[nt][j] = p;
+        l_run[j >> 1] += p;
+      }
+#pragma unroll
+    for (int i = 0; i < 2 * NVT; ++i) {
+      o[i][0] *= corr[0]; o[i][1] *= corr[0]; o[i][2] *= corr[1]; o[i][3] *= corr[1];
+    }
+    uint32_t a[PSPLIT][4];
+#pragma unroll
+    for (int pt = 0; pt < 4; ++pt) {
+      float r0v = s[pt >> 1][(pt & 1) * 2], r1v = s[pt >> 1][(pt & 1) * 2 + 1];
+#pragma unroll
+      for (int sp = 0; sp < PSPLIT; ++sp) a[sp][pt] = split_bf16x2(r0v, r1v);
+    }
+    constexpr int NVG = NVT % 4 == 0 ? 4 : 2;
+#pragma unroll
+    for (int nv0 = 0; nv0 < NVT; nv0 += NVG) {
+      uint32_t b[NVG][4];
+#pragma unroll
+      for (int i = 0; i < NVG; ++i)
+        ldsm_x4_trans(b[i], Vc + (warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * SV + (nv0 + i) * 16 + (lane >> 4) * 8);
+#pragma unroll
+      for (int sp = 0; sp < PSPLIT; ++sp)
+#pragma unroll
+        for (int i = 0; i < NVG; ++i) {
+          mma_bf16(o[2 * (nv0 + i)], a[sp], b[i][0], b[i][1]);
+          mma_bf16(o[2 * (nv0 + i) + 1], a[sp], b[i][2], b[i][3]);
         }
+    }
+    __syncthreads();
+  }
+  // merge the four warps: [warp][row][2 + Dv] floats over the key and value buffers (all tiles are consumed; 4 R (2 + Dv) floats fit for R <= 16)
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
+    l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
+  }
+  float* mg = reinterpret_cast<float*>(Ks);
+  const int row = lane >> 2;  // rows 8 .. 15 hold no head when R <= 8
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    const int rr = row + r * 8;
+    if (rr < R) {
+      float* w = mg + ((size_t)warp * R + rr) * (2 + Dv);
+      if ((lane & 3) == 0) { w[0] = m_run[r]; w[1] = l_run[r]; }
+#pragma unroll
+      for (int i = 0; i < 2 * NVT; ++i) {
+        w[2 + i * 8 + (lane & 3) * 2] = o[i][2 * r];
+        w[2 + i * 8 + (lane & 3) * 2 + 1] = o[i][2 * r + 1];
       }
     }
-  }
-  // the lane groups of a warp hold partial sums over different keys with the same running maximum
-  if (kpi == 2) {
-#pragma unroll
-    for (int mm = 0; mm < MAPS; ++mm)
-#pragma unroll
-      for (int j = 0; j < 8; ++j) acc[mm][j] += __shfl_xor_sync(0xffffffffu, acc[mm][j], 16);
-  }
-  float* mine = smf + (size_t)warp * MAPS * (2 + Dv);
-#pragma unroll
-  for (int mm = 0; mm < MAPS; ++mm) {
-    if (lane == 0) { mine[mm * (2 + Dv)] = m_run[mm]; mine[mm * (2 + Dv) + 1] = l_run[mm]; }
-    if (sub == 0 && vc < vch)
-#pragma unroll
-      for (int j = 0; j < 8; ++j) mine[mm * (2 + Dv) + 2 + vc * 8 + j] = acc[mm][j];
   }
   __syncthreads();
-  if (part != 0) return;
-  // warp `hl` finishes its head: merge the wph partials, combine the maps, normalise
-  float ss = 0.f;
-  float ov[8];  // Dv <= 256: 8 values per lane
+  for (int c = tid; c < R * (Dv + 1); c += 128) {
+    const int r = c / (Dv + 1), d = c - r * (Dv + 1);  // d == Dv: the sum
+    float M = -INFINITY;
 #pragma unroll
-  for (int j = 0; j < 8; ++j) {
-    const int i = lane + 32 * j;
-    ov[j] = 0.f;
-    if (i < Dv) {
-      float am[MAPS];
+    for (int w = 0; w < 4; ++w) M = fmaxf(M, mg[((size_t)w * R + r) * (2 + Dv)]);
+    float acc = 0.f;
 #pragma unroll
-      for (int mm = 0; mm < MAPS; ++mm) {
-        float mx = -INFINITY;
-        for (int pp = 0; pp < wph; ++pp) mx = fmaxf(mx, smf[(size_t)(pp * R + hl) * MAPS * (2 + Dv) + mm * (2 + Dv)]);
-        float num = 0.f, den = 0.f;
-        for (int pp = 0; pp < wph; ++pp) {
-          const float* w = smf + (size_t)(pp * R + hl) * MAPS * (2 + Dv) + mm * (2 + Dv);
-          const float f = exp2f(w[0] - mx);  // a share without keys has maximum -inf and weighs 0
-          num += f * w[2 + i];
-          den += f * w[1];
-        }
-        am[mm] = num / den;
-      }
-      ov[j] = MAPS == 2 ? am[0] - lambda * am[MAPS - 1] : am[0];
-      ss += ov[j] * ov[j];
+    for (int w = 0; w < 4; ++w) {
+      const float* src = mg + ((size_t)w * R + r) * (2 + Dv);
+      const float f = src[0] == -INFINITY ? 0.f : fast_exp2(src[0] - M);
+      acc += f * (d == Dv ? src[1] : src[2 + d]);
     }
+    if (d == Dv) { pout[r * head_step] = M; pout[r * head_step + 1] = acc; }
+    else pout[r * head_step + 2 + d] = acc;
   }
+}
+
+// merge the shares of every (listed token, head, map), then finish the head as multimap_combine_kernel does.  One warp per (token, head).
+template <typename ST>
+__global__ void group_merge_kernel(ST* __restrict__ out, long long out_stride, const float* __restrict__ part, const int* __restrict__ tok_list,
+                                   int n_list, int H, int maps, int Dv, int shares, float lambda, float out_scale, float eps, int head_norm) {
+  const int w = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  if (w >= n_list * H) return;
+  const int li = w / H, h = w - li * H, t = tok_list[li];
+  const float* base = part + ((size_t)li * H + h) * maps * shares * (size_t)(2 + Dv);
+  float ov[8];  // Dv <= 256
+  float ss = 0.f;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) ov[j] = 0.f;
+  for (int mm = 0; mm < maps; ++mm) {
+    const float* pm = base + (size_t)mm * shares * (2 + Dv);
+    float M = -INFINITY;
+    for (int z = 0; z < shares; ++z) M = fmaxf(M, pm[(size_t)z * (2 + Dv)]);
+    float den = 0.f, num[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) num[j] = 0.f;
+    for (int z = 0; z < shares; ++z) {
+      const float* src = pm + (size_t)z * (2 + Dv);
+      if (src[0] == -INFINITY) continue;  // a share without keys wrote no output
+      const float f = fast_exp2(src[0] - M);
+      den += f * src[1];
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        if (lane + 32 * j < Dv) num[j] += f * src[2 + lane + 32 * j];
+    }
+    const float wgt = (mm == 0 ? 1.f : -lambda) / den;  // maps beyond the first enter with -lambda (two maps: a1 - lambda a2)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) ov[j] += wgt * num[j];
+  }
+#pragma unroll
+  for (int j = 0; j < 8; ++j) ss += ov[j] * ov[j];
   ss = warp_sum(ss);
   const float r = head_norm ? out_scale / sqrtf(ss / (float)Dv + eps) : out_scale;
-  __nv_bfloat16* dst = out + (size_t)t * out_stride + (size_t)h * Dv;
+  ST* dst = out + (size_t)t * out_stride + (size_t)h * Dv;
 #pragma unroll
-  for (int j = 0; j < 8; ++j) {
-    const int i = lane + 32 * j;
-    if (i < Dv) dst[i] = __float2bfloat16_rn(ov[j] * r);
-  }
+  for (int j = 0; j < 8; ++j)
+    if (lane + 32 * j < Dv) stf(dst + lane + 32 * j, ov[j] * r);
 }
 
 // ---------------------------------------------------------------------------------------------------------------------------------
@@ -913,6 +1051,32 @@ int launch_tiles(float* scratch, const void* q, long long q_stride, const void* 
   return check_cuda(cudaGetLastError(), "hyb_attention tiles");
 }
 
+// key shares per (token, kv head, map) of the single-token kernel: about four blocks per SM of a 148-SM part in flight
+constexpr int kGroupTargetBlocks = 592, kGroupMaxShares = 32;
+inline int group_shares(int n_tokens, int G, int maps) {
+  const int per = std::max(1, n_tokens * G * maps);
+  return std::max(1, std::min(kGroupMaxShares, (kGroupTargetBlocks + per - 1) / per));
+}
+
+template <int NVT>
+int launch_group(void* out, long long out_stride, float* part, const void* q, long long q_stride, const void* kpool, const void* vpool,
+                 const int* tok_list, int n_list, const int* tok_slot, const int* tok_pos, const int* block_table, int max_blocks, int H, int G,
+                 int maps, int D, float scale, float lambda, float out_scale, float eps, int head_norm, int page, cudaStream_t s) {
+  const size_t smem = ((size_t)(16 + 2 * kTileK) * (D + kPad) + (size_t)2 * kTileK * (NVT * 16 + kPad)) * sizeof(__nv_bfloat16);
+  static bool attr_set[kMaxDevices] = {};
+  if (smem > 48 * 1024 && !attr_set[device_ordinal()]) {
+    if (int rc = check_cuda(cudaFuncSetAttribute(group_attention_kernel<NVT, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024), "group attention smem")) return rc;
+    attr_set[device_ordinal()] = true;
+  }
+  const int shares = group_shares(n_list, G, maps);
+  group_attention_kernel<NVT, 3><<<dim3(n_list, G * maps, shares), 128, smem, s>>>(part, (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)kpool,
+      (const __nv_bfloat16*)vpool, tok_list, tok_slot, tok_pos, block_table, max_blocks, H, G, maps, D, scale, page, shares);
+  const int warps = n_list * H;
+  group_merge_kernel<__nv_bfloat16><<<(warps + 3) / 4, 128, 0, s>>>((__nv_bfloat16*)out, out_stride, part, tok_list, n_list, H, maps, NVT * 16, shares,
+                                                                     lambda, out_scale, eps, head_norm);
+  return check_cuda(cudaGetLastError(), "hyb_attention single tokens");
+}
+
 template <typename ST>
 int launch_delta(void* out, long long out_stride, float* prep, float* o_raw, const void* proj, long long stride, const float* conv_w,
                  float* conv_state, float* state, const float* a_log, const float* dt_bias, const float* norm_w, const int* tok_entry,
@@ -980,6 +1144,14 @@ int qs_hyb_rms_norm(void* out1, void* out2, float* x, const void* add, const flo
   if (tokens_n == 0) return qs::QS_OK;
   cudaStream_t s = (cudaStream_t)stream;
   const int threads = width >= 1024 ? 256 : 128;
+  auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+  if (width % 4 == 0 && al16(out1) && al16(out2) && al16(x) && al16(add) && al16(w1) && al16(w2)) {
+    QS_DT(dtype,
+          (rms_norm2_vec_kernel<__nv_bfloat16><<<tokens_n, threads, 0, s>>>((__nv_bfloat16*)out1, (__nv_bfloat16*)out2, x, (const __nv_bfloat16*)add, w1,
+                                                                             w2, offset, eps, width)),
+          (rms_norm2_vec_kernel<float><<<tokens_n, threads, 0, s>>>((float*)out1, (float*)out2, x, (const float*)add, w1, w2, offset, eps, width)));
+    return check_cuda(cudaGetLastError(), "hyb_rms_norm");
+  }
   QS_DT(dtype,
         (rms_norm2_kernel<__nv_bfloat16><<<tokens_n, threads, 0, s>>>((__nv_bfloat16*)out1, (__nv_bfloat16*)out2, x, (const __nv_bfloat16*)add, w1, w2,
                                                                        offset, eps, width)),
@@ -1001,6 +1173,11 @@ int qs_hyb_gelu_tanh_mul(void* out, int64_t out_stride, const void* in, int toke
   QS_REQUIRE(out && in, "hyb_gelu_tanh_mul: null tensor");
   if (tokens_n == 0) return qs::QS_OK;
   cudaStream_t s = (cudaStream_t)stream;
+  if (dtype == QS_DTYPE_BF16 && ff % 8 == 0 && out_stride % 8 == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0 &&
+      (reinterpret_cast<uintptr_t>(in) & 15) == 0) {
+    gelu_tanh_mul_bf16x8_kernel<<<dim3(tokens_n, (ff / 8 + 255) / 256), 256, 0, s>>>((__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)in, ff);
+    return check_cuda(cudaGetLastError(), "hyb_gelu_tanh_mul");
+  }
   dim3 grid(tokens_n, (ff + 255) / 256);
   QS_DT(dtype, (gelu_tanh_mul_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)in, ff)),
         (gelu_tanh_mul_kernel<float><<<grid, 256, 0, s>>>((float*)out, out_stride, (const float*)in, ff)));
@@ -1044,6 +1221,13 @@ int qs_hyb_attention_fast_supported(int dtype, int heads, int kv_heads, int maps
   return fast_attention_supported(dtype, heads, kv_heads, maps, dim, vdim, q_stride) ? 1 : 0;
 }
 
+int64_t qs_hyb_attention_scratch_floats(int tokens, int heads, int kv_heads, int maps, int vdim) {
+  // per-map outputs of the tiles [tokens][heads][maps][vdim], then the single tokens' shares [tokens][heads][maps][shares][2 + vdim]
+  const int64_t per = std::max(1, kv_heads * maps);
+  const int64_t rows = (int64_t)tokens + (kGroupTargetBlocks + per - 1) / per;  // tokens x shares never exceeds this
+  return (int64_t)tokens * heads * maps * vdim + rows * heads * maps * (2 + vdim);
+}
+
 int qs_hyb_attention_fast(void* out, int64_t out_stride, const void* q, int64_t q_stride, const void* kpool, const void* vpool,
                           const int32_t* tok_slot, const int32_t* tok_pos, const int32_t* block_table, int max_blocks, const int32_t* tile_entry,
                           const int32_t* tile_row0, int n_tiles, const int32_t* long_tokens, int n_long, const int32_t* short_tokens, int n_short,
@@ -1054,7 +1238,7 @@ int qs_hyb_attention_fast(void* out, int64_t out_stride, const void* q, int64_t 
   QS_REQUIRE(fast_attention_supported(dtype, heads, kv_heads, maps, dim, vdim, q_stride), "hyb_attention_fast: shape not supported (use qs_hyb_attention)");
   QS_REQUIRE(n_tiles == 0 || (tile_entry && tile_row0 && long_tokens && scratch && entry_start && entry_len && entry_slot && entry_pos0),
              "hyb_attention_fast: null tile table");
-  QS_REQUIRE(n_short == 0 || short_tokens, "hyb_attention_fast: null token list");
+  QS_REQUIRE(n_short == 0 || (short_tokens && scratch), "hyb_attention_fast: null token list");
   cudaStream_t s = (cudaStream_t)stream;
   if (n_tiles > 0) {
     int rc = 0;
@@ -1074,28 +1258,19 @@ int qs_hyb_attention_fast(void* out, int64_t out_stride, const void* q, int64_t 
                                                                           lambda, out_scale, eps, head_norm);
   }
   if (n_short > 0) {
-    // warps per head: enough warps in flight to hide the latency of the key walk when the batch is small (about 48 per SM wanted),
-    // within 1024 threads and 48 KB of merge space per block
-    const int R = heads / kv_heads;
-    const size_t per_warp = (size_t)maps * (2 + vdim) * sizeof(float), q_bytes = 0;
-    int wph = (48 * num_sms() + n_short * heads - 1) / (n_short * heads);
-    wph = std::max(1, std::min(wph, 16 / R));  // at most 512 threads: 65 registers per thread
-    while (wph > 1 && q_bytes + (size_t)R * wph * per_warp > 48 * 1024) --wph;
-    const int nw = R * wph;
-    const size_t smem = q_bytes + (size_t)nw * per_warp;
-    QS_REQUIRE(smem <= 48 * 1024, "hyb_attention_fast: head group too large for the single-token kernel");
-    dim3 grid(n_short, kv_heads);
-    const int qch = (maps * dim / 8 + 31) / 32;
-#define QS_DEC(MAPS, QCH)                                                                                                                          \
-  decode_vec_attention_kernel<MAPS, QCH><<<grid, nw * 32, smem, s>>>((__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)q, q_stride,         \
-      (const __nv_bfloat16*)kpool, (const __nv_bfloat16*)vpool, short_tokens, tok_slot, tok_pos, block_table, max_blocks, heads, kv_heads, dim, \
-      vdim, wph, scale, lambda, out_scale, eps, head_norm, page_size)
-    if (maps == 2) {
-      if (qch <= 1) QS_DEC(2, 1); else if (qch <= 2) QS_DEC(2, 2); else QS_DEC(2, 4);
-    } else {
-      if (qch <= 1) QS_DEC(1, 1); else if (qch <= 2) QS_DEC(1, 2); else QS_DEC(1, 4);
+    int rc = 0;
+    float* part = scratch + (size_t)(n_long + n_short) * heads * maps * vdim;  // behind the per-map outputs of the tiles
+#define QS_GROUP(NVT) rc = launch_group<NVT>(out, out_stride, part, q, q_stride, kpool, vpool, short_tokens, n_short, tok_slot, tok_pos, block_table, \
+                                             max_blocks, heads, kv_heads, maps, dim, scale, lambda, out_scale, eps, head_norm, page_size, s)
+    switch (vdim / 16) {
+      case 2: QS_GROUP(2); break;
+      case 4: QS_GROUP(4); break;
+      case 6: QS_GROUP(6); break;
+      case 8: QS_GROUP(8); break;
+      default: QS_GROUP(16); break;
     }
-#undef QS_DEC
+#undef QS_GROUP
+    if (rc) return rc;
   }
   return check_cuda(cudaGetLastError(), "hyb_attention_fast");
 }

@@ -133,7 +133,8 @@ class MultiMapAttentionMixer:
             self.lam, self.out_scale = 0.0, 1.0
 
     def scratch_floats(self, tokens: int) -> int:
-        return tokens * self.m.heads * self.m.maps * self.m.vdim  # per-map outputs of the tiled prompt kernel
+        # per-map outputs of the tiled prompt kernel and the key shares of the single-token kernel
+        return int(lib.qs_hyb_attention_scratch_floats(tokens, self.m.heads, self.m.kv_heads, self.m.maps, self.m.vdim))
 
     def run(self, proj: torch.Tensor, out: torch.Tensor, b: StepBatch, run_cache: dict, page_size: int, scratch, dt: int, stream) -> None:
         m = self.m
@@ -142,7 +143,7 @@ class MultiMapAttentionMixer:
                                      run_cache["k"].data_ptr(), run_cache["v"].data_ptr(), self.inv_freq.data_ptr(), self.amp, b.n_tokens,
                                      m.heads, m.kv_heads, m.maps, m.dim, m.vdim, m.rot.dims, page_size, dt, stream))
         if fast:
-            # prompt portions as 64-row tiles on the tensor cores, single tokens and short portions on the vectorised kernel
+            # prompt portions as 64-row tiles on the tensor cores, single tokens and short portions with a head group as the tile's rows
             check(lib.qs_hyb_attention_fast(out.data_ptr(), out.stride(0), proj.data_ptr(), proj.stride(0), run_cache["k"].data_ptr(),
                                             run_cache["v"].data_ptr(), _p(b.tok_slot), _p(b.tok_pos), _p(b.block_table), b.block_table.shape[1],
                                             _p(b.tile_entry), _p(b.tile_row0), b.n_tiles, _p(b.long_tokens), b.n_long, _p(b.short_tokens), b.n_short,

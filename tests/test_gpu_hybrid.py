@@ -245,7 +245,7 @@ def test_one_key_stands_out(dev, needle, decode):
 @pytest.mark.parametrize("needle", [0, 63, 64, 128, 300, 510])
 @pytest.mark.parametrize("decode", [False, True])
 def test_one_key_stands_out_on_the_fast_kernels(dev, needle, decode):
-    """The same in bfloat16 with head sizes the tensor-core prompt kernel and the vectorised single-token kernel take."""
+    """The same in bfloat16 with head sizes the tensor-core prompt and single-token kernels take."""
     n = 512
     cfg, w, toks = _needle_model(n, needle, dim=16, vdim=32)
     want = O.forward(cfg, w, toks)[-1:]
@@ -262,7 +262,7 @@ def test_one_key_stands_out_on_the_fast_kernels(dev, needle, decode):
 @pytest.mark.parametrize("shape", [(4, 2, 2, 16, 32), (4, 4, 2, 48, 96), (8, 2, 2, 32, 64), (2, 1, 1, 64, 128), (3, 3, 2, 16, 256), (16, 1, 2, 16, 32)],
                          ids=lambda s: "H%d-G%d-maps%d-D%d-Dv%d" % s)
 def test_fast_attention_kernels_match_the_plain_kernel(dev, shape):
-    """Same bfloat16 inputs and cache through the tensor-core / vectorised kernels and through the plain kernel: prompt portions with and
+    """Same bfloat16 inputs and cache through the tensor-core kernels and through the plain kernel: prompt portions with and
     without context, portions that end inside a page, short portions and single tokens in one batch."""
     from qserve_b200.hybrid import MultiMapAttentionMixer, StepBatch
     from qserve_b200.modelcfg import AttentionMixerConfig, RotaryConfig
@@ -282,7 +282,10 @@ def test_fast_attention_kernels_match_the_plain_kernel(dev, shape):
     # step 1: context; step 2: continuation of every sequence with another portion size
     steps = [[(0, 0, -1, [0] * 200), (1, 0, -1, [0] * 70), (2, 0, -1, [0] * 3), (3, 0, -1, [0] * 16)],
              [(0, 200, 0, [0] * 1), (1, 70, 0, [0] * 130), (2, 3, 0, [0] * 15), (3, 16, 0, [0] * 64)],
-             [(0, 201, 0, [0] * 90), (1, 200, 0, [0] * 1), (2, 18, 0, [0] * 1), (3, 80, 0, [0] * 17)]]
+             [(0, 201, 0, [0] * 90), (1, 200, 0, [0] * 1), (2, 18, 0, [0] * 1), (3, 80, 0, [0] * 17)],
+             # many short portions: the single-token kernel gives each block several key tiles, or none
+             [(0, 291, 0, [0] * 15), (1, 201, 0, [0] * 15), (2, 19, 0, [0] * 15), (3, 97, 0, [0] * 15)],
+             [(0, 306, 0, [0] * 1), (3, 112, 0, [0] * 1)]]
     for entries in steps:
         b = StepBatch.build(entries, table, dev)
         T = b.n_tokens
