@@ -437,13 +437,17 @@ __global__ void __launch_bounds__(128) tile_attention_kernel(
   const float scale_log2 = scale * 1.4426950408889634f;
   const int qrow = warp * 16 + (lane >> 2);  // this thread's rows: qrow, qrow + 8
   // key / value tiles are double-buffered: tile kt + 1 streams in with cp.async while tile kt is multiplied
-  // two threads per key row, alternating 16-byte chunks: one block-table lookup per thread and tile
-  auto load_kv = [&](int kt, int buf) {
-    const int r = tid >> 1, kp = kt * kTileK + r;
+  // two threads per key row, alternating 16-byte chunks: one block-table lookup per thread and tile, made one tile ahead of its use so
+  // that the lookup's latency hides behind a tile of arithmetic
+  auto cell_of = [&](int kt) -> long long {
+    const int kp = kt * kTileK + (tid >> 1);
+    return kp <= last_qpos ? (long long)bt[kp / page] * page + kp % page : -1;
+  };
+  auto load_kv = [&](int kt, int buf, long long cell) {
+    const int r = tid >> 1;
     __nv_bfloat16* Kd = Ks + (size_t)buf * kTileK * SD + r * SD;
     __nv_bfloat16* Vd = Vs + (size_t)buf * kTileK * SV + r * SV;
-    if (kp <= last_qpos) {
-      const size_t cell = (size_t)bt[kp / page] * page + kp % page;
+    if (cell >= 0) {
       const __nv_bfloat16* ksrc = kpool + ((cell * G + g) * maps + m) * (size_t)D;
       const __nv_bfloat16* vsrc = vpool + (cell * G + g) * (size_t)Dv;
       for (int cc = tid & 1; cc < dch; cc += 2) cp_async16(Kd + cc * 8, ksrc + cc * 8);
@@ -456,10 +460,12 @@ __global__ void __launch_bounds__(128) tile_attention_kernel(
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
   };
-  load_kv(0, 0);
+  load_kv(0, 0, cell_of(0));
+  long long cell_next = n_kt > 1 ? cell_of(1) : -1;
   for (int kt = 0; kt < n_kt; ++kt) {
     if (kt + 1 < n_kt) {
-      load_kv(kt + 1, (kt + 1) & 1);
+      load_kv(kt + 1, (kt + 1) & 1, cell_next);
+      if (kt + 2 < n_kt) cell_next = cell_of(kt + 2);
       asm volatile("cp.async.wait_group 1;" ::: "memory");
     } else {
       asm volatile("cp.async.wait_group 0;" ::: "memory");
@@ -629,13 +635,17 @@ __global__ void __launch_bounds__(128) group_attention_kernel(
   for (int i = 0; i < 2 * NVT; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
   const float scale_log2 = scale * 1.4426950408889634f;
-  // two threads per key row, alternating 16-byte chunks: one block-table lookup per thread and tile
-  auto load_kv = [&](int kt, int buf) {
-    const int r = tid >> 1, kp = kt * kTileK + r;
+  // two threads per key row, alternating 16-byte chunks: one block-table lookup per thread and tile, made one tile ahead of its use so
+  // that the lookup's latency hides behind a tile of arithmetic
+  auto cell_of = [&](int kt) -> long long {
+    const int kp = kt * kTileK + (tid >> 1);
+    return kp <= pos ? (long long)bt[kp / page] * page + kp % page : -1;
+  };
+  auto load_kv = [&](int kt, int buf, long long cell) {
+    const int r = tid >> 1;
     __nv_bfloat16* Kd = Ks + (size_t)buf * kTileK * SD + r * SD;
     __nv_bfloat16* Vd = Vs + (size_t)buf * kTileK * SV + r * SV;
-    if (kp <= pos) {
-      const size_t cell = (size_t)bt[kp / page] * page + kp % page;
+    if (cell >= 0) {
       const __nv_bfloat16* ksrc = kpool + ((cell * G + g) * maps + m) * (size_t)D;
       const __nv_bfloat16* vsrc = vpool + (cell * G + g) * (size_t)Dv;
       for (int cc = tid & 1; cc < dch; cc += 2) cp_async16(Kd + cc * 8, ksrc + cc * 8);
@@ -648,11 +658,13 @@ __global__ void __launch_bounds__(128) group_attention_kernel(
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
   };
-  load_kv(kt0, 0);
+  load_kv(kt0, 0, cell_of(kt0));
+  long long cell_next = kt0 + 1 < kt1 ? cell_of(kt0 + 1) : -1;
   for (int kt = kt0; kt < kt1; ++kt) {
     const int buf = (kt - kt0) & 1;
     if (kt + 1 < kt1) {
-      load_kv(kt + 1, buf ^ 1);
+      load_kv(kt + 1, buf ^ 1, cell_next);
+      if (kt + 2 < kt1) cell_next = cell_of(kt + 2);
       asm volatile("cp.async.wait_group 1;" ::: "memory");
     } else {
       asm volatile("cp.async.wait_group 0;" ::: "memory");
