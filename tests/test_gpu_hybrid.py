@@ -350,3 +350,38 @@ def test_sampling_is_seeded_and_respects_top_k(dev):
     top3 = torch.topk(logits, 3).indices
     assert all(int(a[i]) in top3[i].tolist() for i in range(5))
     assert torch.equal(sample(logits, [SamplingParams()] * 5), logits.argmax(-1))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("width,ff", [(40, 48), (37, 21), (256, 264), (1030, 12)])
+def test_norm_and_activation_kernels_on_aligned_and_odd_rows(dev, dtype, width, ff):
+    """The stream's norm (with the previous update added in place, one or two gains) and the gated activation, on widths that take the
+    16-byte kernels and on widths that do not, against the formulas in float64."""
+    from qserve_b200._lib import check, lib
+
+    g = torch.Generator().manual_seed(width)
+    T, dt = 7, 0 if dtype == torch.bfloat16 else 1
+    s = torch.cuda.current_stream().cuda_stream
+    x = torch.randn(T, width, generator=g).to(dev)
+    add = torch.randn(T, width, generator=g).to(dtype).to(dev)
+    w1, w2 = (torch.randn(width, generator=g) * 0.3).to(dev), (torch.randn(width, generator=g) * 0.3).to(dev)
+    for use_add, two in ((True, True), (False, True), (True, False)):
+        xs = x.clone()
+        o1, o2 = torch.zeros(T, width, dtype=dtype, device=dev), torch.zeros(T, width, dtype=dtype, device=dev)
+        check(lib.qs_hyb_rms_norm(o1.data_ptr(), o2.data_ptr() if two else None, xs.data_ptr(), add.data_ptr() if use_add else None, w1.data_ptr(),
+                                  w2.data_ptr() if two else None, 1.0, 1e-5, T, width, dt, s))
+        want_x = x.double() + (add.double() if use_add else 0.0)
+        n = want_x / (want_x.pow(2).mean(-1, keepdim=True) + 1e-5).sqrt()
+        tol = 1e-5 if dtype == torch.float32 else 2.0 ** -8
+        assert torch.allclose(xs.double(), want_x, atol=1e-6)
+        assert row_err(o1, n * (1.0 + w1.double())) < tol
+        if two:
+            assert row_err(o2, n * (1.0 + w2.double())) < tol
+    gu = (torch.randn(T, 2 * ff, generator=g) * 2.0).to(dtype).to(dev)
+    for off in (0, 8, 3):  # the output lands at a column offset of a wider row, as in the concatenated input of the output projection
+        out = torch.zeros(T, off + ff, dtype=dtype, device=dev)
+        check(lib.qs_hyb_gelu_tanh_mul(out.data_ptr() + off * out.element_size(), out.stride(0), gu.data_ptr(), T, ff, dt, s))
+        z, u = gu[:, :ff].double(), gu[:, ff:].double()
+        want = 0.5 * z * (1.0 + torch.tanh(math.sqrt(2.0 / math.pi) * (z + 0.044715 * z ** 3))) * u
+        assert row_err(out[:, off:], want) < (1e-5 if dtype == torch.float32 else 2.0 ** -8)
+        assert float(out[:, :off].abs().sum()) == 0.0
