@@ -669,7 +669,7 @@ def hybrid_block(args):
         dlt = DeltaMixerConfig(H, G, D, D, 4)
         cfg = HybridConfig("Rizurax", V, W, 1e-5, tuple(HybridLayerConfig(t, m, MlpConfig("dense", FF)) for t, m in
                                                        (("attention", att), ("delta", dlt), ("attention", att), ("delta", dlt))),
-                           pair_buckets=4093, pair_mul_prev=127, pair_mul_cur=7)
+                           pair_buckets=4093, pair_mul_prev=131, pair_mul_cur=11)
         model = HybridDecoder(cfg, random_weights(cfg, 0, dev), torch.bfloat16, dev)
         eng = Engine(model, max_tokens=B * (CTX + 64), max_seqs=B)
         g = torch.Generator().manual_seed(0)
