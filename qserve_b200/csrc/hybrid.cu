@@ -911,7 +911,7 @@ __device__ __forceinline__ float part_sum(float v) {
   return v;
 }
 
-template <int DP, int PARTS, int CH>
+template <int DP, int PARTS, int CH, bool VEC>  // VEC: rows of `prep`, D and Dv are multiples of 4 floats: stage with 16-byte copies
 __global__ void __launch_bounds__(128) delta_scan_kernel(float* __restrict__ o_raw, const float* __restrict__ prep, float* __restrict__ state,
                                                          const int* __restrict__ entry_start, const int* __restrict__ entry_len,
                                                          const int* __restrict__ entry_slot, const int* __restrict__ entry_pos0, int H, int G, int D,
@@ -932,6 +932,41 @@ __global__ void __launch_bounds__(128) delta_scan_kernel(float* __restrict__ o_r
     S[j] = (live && !fresh && i < D) ? Sg[(size_t)i * Dv + col] : 0.f;
   }
   auto stage = [&](int chunk, int buf) {
+    if (VEC) {
+      constexpr int QV = Q / 4, NQK = 2 * PARTS * QV, NV = COLS / 4, ITEMS = NQK + NV + 2;
+      for (int idx = tid; idx < CH * ITEMS; idx += 128) {
+        const int tk = idx / ITEMS, j = idx - tk * ITEMS, t = chunk * CH + tk;
+        float* base = sm + (size_t)(buf * CH + tk) * ROW;
+        const float* row = prep + (size_t)(s0 + min(t, n - 1)) * P;
+        float* dst;
+        const float* src = nullptr;
+        int bytes = 16;
+        if (j < NQK) {
+          const int which = j / (PARTS * QV), rem = j - which * (PARTS * QV), pp = rem / QV, w4 = rem - pp * QV, i = pp * Q + w4 * 4;
+          dst = base + which * QK + pp * SEG + w4 * 4;
+          if (i < D) src = row + (size_t)(which * G + g) * D + i;
+        } else if (j < NQK + NV) {
+          const int c4 = (j - NQK) * 4, c = cg * COLS + c4;
+          dst = base + 2 * QK + c4;
+          if (c < Dv) src = row + 2 * G * D + (size_t)h * Dv + c;
+        } else {
+          const int w = j - NQK - NV;  // beta, decay
+          dst = base + 2 * QK + COLS + w;
+          src = row + C + w * H + h;
+          bytes = 4;
+        }
+        if (t >= n) src = nullptr;
+        if (src != nullptr) {
+          if (bytes == 16) cp_async16(dst, src); else cp_async4(dst, src);
+        } else if (bytes == 16) {
+          *reinterpret_cast<float4*>(dst) = make_float4(0.f, 0.f, 0.f, 0.f);
+        } else {
+          *dst = 0.f;
+        }
+      }
+      asm volatile("cp.async.commit_group;" ::: "memory");
+      return;
+    }
     for (int idx = tid; idx < CH * ROW; idx += 128) {
       const int tk = idx / ROW, j = idx - tk * ROW, t = chunk * CH + tk;
       float* dst = sm + (size_t)(buf * CH + tk) * ROW + j;
@@ -1102,14 +1137,23 @@ int launch_delta(void* out, long long out_stride, float* prep, float* o_raw, con
   if (taps > 1)
     delta_conv_state_kernel<ST><<<dim3((C + 127) / 128, E), 128, 0, s>>>(conv_state, (const ST*)proj, stride, entry_start, entry_len, entry_slot,
                                                                           entry_pos0, C, taps);
+  // 16-byte staging needs every q / k / v run of a prepared row on a 16-byte boundary
+  const bool vec = D % 4 == 0 && Dv % 4 == 0 && (C + 2 * H) % 4 == 0 && (reinterpret_cast<uintptr_t>(prep) & 15) == 0;
   // rows of a column per thread: all of them up to 64 (a warp then reads q / k as broadcasts), 64 above
 #define QS_SCAN(DP, PARTS, CH)                                                                                                                \
   do {                                                                                                                                        \
     constexpr int cols = 128 / PARTS;                                                                                                         \
     const size_t sm = (size_t)2 * CH * (2 * PARTS * (DP / PARTS + 4) + cols + 4) * sizeof(float);                                             \
     dim3 grid(E, H, (Dv + cols - 1) / cols);                                                                                                  \
-    if (sm > 48 * 1024) cudaFuncSetAttribute(delta_scan_kernel<DP, PARTS, CH>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);         \
-    delta_scan_kernel<DP, PARTS, CH><<<grid, 128, sm, s>>>(o_raw, prep, state, entry_start, entry_len, entry_slot, entry_pos0, H, G, D, Dv); \
+    if (vec) {                                                                                                                              \
+      if (sm > 48 * 1024) cudaFuncSetAttribute(delta_scan_kernel<DP, PARTS, CH, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm); \
+      delta_scan_kernel<DP, PARTS, CH, true><<<grid, 128, sm, s>>>(o_raw, prep, state, entry_start, entry_len, entry_slot, entry_pos0, H, G,  \
+                                                                   D, Dv);                                                                    \
+    } else {                                                                                                                                  \
+      if (sm > 48 * 1024) cudaFuncSetAttribute(delta_scan_kernel<DP, PARTS, CH, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);\
+      delta_scan_kernel<DP, PARTS, CH, false><<<grid, 128, sm, s>>>(o_raw, prep, state, entry_start, entry_len, entry_slot, entry_pos0, H, G, \
+                                                                    D, Dv);                                                                   \
+    }                                                                                                                                         \
   } while (0)
   if (D <= 16) QS_SCAN(16, 1, 16);
   else if (D <= 32) QS_SCAN(32, 1, 16);
