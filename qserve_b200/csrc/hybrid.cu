@@ -364,7 +364,7 @@ __global__ void __launch_bounds__(kAttnThreads) paged_multimap_attention_kernel(
 
 // ---------------------------------------------------------------------------------------------------------------------------------
 // Prompt portions on the tensor cores (bfloat16 storage).  One block = 64 consecutive query rows of one entry x one (head, map); keys are
-// walked in tiles of 64 positions through the block table.  S = Q K^T with mma.sync m16n8k16 (bf16 operands are exact, fp32 accumulation: the
+// walked in tiles of KT (32 or 64) positions through the block table.  S = Q K^T with mma.sync m16n8k16 (bf16 operands are exact, fp32 accumulation: the
 // scores are fp32), online softmax in fp32 registers, and P V with the fp32 weights split into PSPLIT bfloat16 terms (p = hi + mid + lo, 24
 // mantissa bits) so that the weights enter the product at fp32 precision although the tensor cores take 16-bit operands.  The normalised
 // per-map outputs go to an fp32 scratch [token][head][map][Dv]; multimap_combine_kernel finishes the head.
@@ -403,8 +403,8 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
-template <int NVT, int PSPLIT>  // NVT = Dv / 16
-__global__ void __launch_bounds__(128) tile_attention_kernel(
+template <int NVT, int PSPLIT, int KT>  // NVT = Dv / 16, KT keys per tile (64, or 32: less shared memory and fewer registers, 3 blocks per SM)
+__global__ void __launch_bounds__(128, KT == 32 ? 3 : 2) tile_attention_kernel(
     float* __restrict__ a_out, const __nv_bfloat16* __restrict__ q, long long q_stride, const __nv_bfloat16* __restrict__ kpool,
     const __nv_bfloat16* __restrict__ vpool, const int* __restrict__ tile_entry, const int* __restrict__ tile_row0,
     const int* __restrict__ entry_start, const int* __restrict__ entry_len, const int* __restrict__ entry_slot, const int* __restrict__ entry_pos0,
@@ -414,7 +414,7 @@ __global__ void __launch_bounds__(128) tile_attention_kernel(
   const int SD = D + kPad, SV = Dv + kPad;
   __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smraw);
   __nv_bfloat16* Ks = Qs + kTileQ * SD;
-  __nv_bfloat16* Vs = Ks + 2 * kTileK * SD;  // two key buffers, then two value buffers
+  __nv_bfloat16* Vs = Ks + 2 * KT * SD;  // two key buffers, then two value buffers
   const int tile = blockIdx.x, hm = blockIdx.y, h = hm / maps, m = hm - h * maps, g = h / (H / G);
   const int e = tile_entry[tile], r0 = tile_row0[tile];
   const int n_rows = min(kTileQ, entry_len[e] - r0);
@@ -433,30 +433,31 @@ __global__ void __launch_bounds__(128) tile_attention_kernel(
   for (int i = 0; i < 2 * NVT; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
   const int last_qpos = qpos0 + n_rows - 1;
-  const int n_kt = last_qpos / kTileK + 1;
+  const int n_kt = last_qpos / KT + 1;
   const float scale_log2 = scale * 1.4426950408889634f;
   const int qrow = warp * 16 + (lane >> 2);  // this thread's rows: qrow, qrow + 8
   // key / value tiles are double-buffered: tile kt + 1 streams in with cp.async while tile kt is multiplied
-  // two threads per key row, alternating 16-byte chunks: one block-table lookup per thread and tile, made one tile ahead of its use so
+  constexpr int TPR = 128 / KT;
+  // TPR threads per key row, alternating 16-byte chunks: one block-table lookup per thread and tile, made one tile ahead of its use so
   // that the lookup's latency hides behind a tile of arithmetic
   auto cell_of = [&](int kt) -> long long {
-    const int kp = kt * kTileK + (tid >> 1);
+    const int kp = kt * KT + tid / TPR;
     return kp <= last_qpos ? (long long)bt[kp / page] * page + kp % page : -1;
   };
   auto load_kv = [&](int kt, int buf, long long cell) {
-    const int r = tid >> 1;
-    __nv_bfloat16* Kd = Ks + (size_t)buf * kTileK * SD + r * SD;
-    __nv_bfloat16* Vd = Vs + (size_t)buf * kTileK * SV + r * SV;
+    const int r = tid / TPR;
+    __nv_bfloat16* Kd = Ks + (size_t)buf * KT * SD + r * SD;
+    __nv_bfloat16* Vd = Vs + (size_t)buf * KT * SV + r * SV;
     if (cell >= 0) {
       const __nv_bfloat16* ksrc = kpool + ((cell * G + g) * maps + m) * (size_t)D;
       const __nv_bfloat16* vsrc = vpool + (cell * G + g) * (size_t)Dv;
-      for (int cc = tid & 1; cc < dch; cc += 2) cp_async16(Kd + cc * 8, ksrc + cc * 8);
+      for (int cc = tid % TPR; cc < dch; cc += TPR) cp_async16(Kd + cc * 8, ksrc + cc * 8);
 #pragma unroll
-      for (int cc = tid & 1; cc < Dv / 8; cc += 2) cp_async16(Vd + cc * 8, vsrc + cc * 8);
+      for (int cc = tid % TPR; cc < Dv / 8; cc += TPR) cp_async16(Vd + cc * 8, vsrc + cc * 8);
     } else {
-      for (int cc = tid & 1; cc < dch; cc += 2) *reinterpret_cast<uint4*>(Kd + cc * 8) = make_uint4(0, 0, 0, 0);
+      for (int cc = tid % TPR; cc < dch; cc += TPR) *reinterpret_cast<uint4*>(Kd + cc * 8) = make_uint4(0, 0, 0, 0);
 #pragma unroll
-      for (int cc = tid & 1; cc < Dv / 8; cc += 2) *reinterpret_cast<uint4*>(Vd + cc * 8) = make_uint4(0, 0, 0, 0);
+      for (int cc = tid % TPR; cc < Dv / 8; cc += TPR) *reinterpret_cast<uint4*>(Vd + cc * 8) = make_uint4(0, 0, 0, 0);
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
   };
@@ -471,32 +472,32 @@ __global__ void __launch_bounds__(128) tile_attention_kernel(
       asm volatile("cp.async.wait_group 0;" ::: "memory");
     }
     __syncthreads();
-    const __nv_bfloat16* Kc = Ks + (size_t)(kt & 1) * kTileK * SD;
-    const __nv_bfloat16* Vc = Vs + (size_t)(kt & 1) * kTileK * SV;
-    float s[8][4];
+    const __nv_bfloat16* Kc = Ks + (size_t)(kt & 1) * KT * SD;
+    const __nv_bfloat16* Vc = Vs + (size_t)(kt & 1) * KT * SV;
+    float s[KT / 8][4];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+    for (int i = 0; i < KT / 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
     for (int ks = 0; ks < D; ks += 16) {
       uint32_t a[4];
       ldsm_x4(a, Qs + (warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * SD + ks + (lane >> 4) * 8);
 #pragma unroll
-      for (int np = 0; np < 4; ++np) {
+      for (int np = 0; np < KT / 16; ++np) {
         uint32_t b[4];
         ldsm_x4(b, Kc + (np * 16 + (lane & 7) + (lane >> 4) * 8) * SD + ks + ((lane >> 3) & 1) * 8);
         mma_bf16(s[2 * np], a, b[0], b[1]);
         mma_bf16(s[2 * np + 1], a, b[2], b[3]);
       }
     }
-    // scale, causal mask, online softmax (rows qrow and qrow + 8; a row's 64 columns live in the 4 lanes of a quad)
+    // scale, causal mask, online softmax (rows qrow and qrow + 8; a row's columns live in the 4 lanes of a quad)
     float mx[2] = {-INFINITY, -INFINITY};
-    const bool diagonal = kt * kTileK + kTileK - 1 > qpos0 + warp * 16;
+    const bool diagonal = kt * KT + KT - 1 > qpos0 + warp * 16;
 #pragma unroll
-    for (int nt = 0; nt < 8; ++nt)
+    for (int nt = 0; nt < KT / 8; ++nt)
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         float v = s[nt][j] * scale_log2;
         if (diagonal) {  // warp-uniform: only tiles that reach past this warp's first row need the causal mask
-          const int kpos = kt * kTileK + nt * 8 + (lane & 3) * 2 + (j & 1);
+          const int kpos = kt * KT + nt * 8 + (lane & 3) * 2 + (j & 1);
           const int qp = qpos0 + qrow + (j >> 1) * 8;
           if (kpos > qp) v = -INFINITY;
         }
@@ -514,7 +515,7 @@ __global__ void __launch_bounds__(128) tile_attention_kernel(
       l_run[r] *= corr[r];
     }
 #pragma unroll
-    for (int nt = 0; nt < 8; ++nt)
+    for (int nt = 0; nt < KT / 8; ++nt)
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         const float mm = m_run[j >> 1];
@@ -530,7 +531,7 @@ __global__ void __launch_bounds__(128) tile_attention_kernel(
     // accumulator are 2 NVG instructions apart
     constexpr int NVG = NVT % 4 == 0 ? 4 : 2;
 #pragma unroll
-    for (int kk = 0; kk < 4; ++kk) {  // 16 keys per step
+    for (int kk = 0; kk < KT / 16; ++kk) {  // 16 keys per step
       uint32_t a[PSPLIT][4];
 #pragma unroll
       for (int part = 0; part < 4; ++part) {
@@ -1083,17 +1084,20 @@ bool fast_attention_supported(int dtype, int heads, int kv_heads, int maps, int 
   return true;
 }
 
-template <int NVT>
+// keys per prompt tile: 32 keeps a block at 52 KB and 168 registers for head sizes up to 128, so that three blocks share an SM
+constexpr int kTileKeysPrompt = 32;
+
+template <int NVT, int KT>
 int launch_tiles(float* scratch, const void* q, long long q_stride, const void* kpool, const void* vpool, const int* tile_entry, const int* tile_row0,
                  int n_tiles, const int* entry_start, const int* entry_len, const int* entry_slot, const int* entry_pos0, const int* block_table,
                  int max_blocks, int H, int G, int maps, int D, float scale, int page, cudaStream_t s) {
-  const size_t smem = ((size_t)3 * kTileQ * (D + kPad) + (size_t)2 * kTileK * (NVT * 16 + kPad)) * sizeof(__nv_bfloat16);
+  const size_t smem = ((size_t)(kTileQ + 2 * KT) * (D + kPad) + (size_t)2 * KT * (NVT * 16 + kPad)) * sizeof(__nv_bfloat16);
   static bool attr_set[kMaxDevices] = {};
   if (smem > 48 * 1024 && !attr_set[device_ordinal()]) {
-    if (int rc = check_cuda(cudaFuncSetAttribute(tile_attention_kernel<NVT, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024), "tile attention smem")) return rc;
+    if (int rc = check_cuda(cudaFuncSetAttribute(tile_attention_kernel<NVT, 3, KT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024), "tile attention smem")) return rc;
     attr_set[device_ordinal()] = true;
   }
-  tile_attention_kernel<NVT, 3><<<dim3(n_tiles, H * maps), 128, smem, s>>>(scratch, (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)kpool,
+  tile_attention_kernel<NVT, 3, KT><<<dim3(n_tiles, H * maps), 128, smem, s>>>(scratch, (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)kpool,
       (const __nv_bfloat16*)vpool, tile_entry, tile_row0, entry_start, entry_len, entry_slot, entry_pos0, block_table, max_blocks, H, G, maps, D, scale, page);
   return check_cuda(cudaGetLastError(), "hyb_attention tiles");
 }
@@ -1298,14 +1302,14 @@ int qs_hyb_attention_fast(void* out, int64_t out_stride, const void* q, int64_t 
   cudaStream_t s = (cudaStream_t)stream;
   if (n_tiles > 0) {
     int rc = 0;
-#define QS_TILES(NVT) rc = launch_tiles<NVT>(scratch, q, q_stride, kpool, vpool, tile_entry, tile_row0, n_tiles, entry_start, entry_len, entry_slot, \
+#define QS_TILES(NVT, KT) rc = launch_tiles<NVT, KT>(scratch, q, q_stride, kpool, vpool, tile_entry, tile_row0, n_tiles, entry_start, entry_len, entry_slot, \
                                              entry_pos0, block_table, max_blocks, heads, kv_heads, maps, dim, scale, page_size, s)
     switch (vdim / 16) {
-      case 2: QS_TILES(2); break;
-      case 4: QS_TILES(4); break;
-      case 6: QS_TILES(6); break;
-      case 8: QS_TILES(8); break;
-      default: QS_TILES(16); break;
+      case 2: QS_TILES(2, kTileKeysPrompt); break;
+      case 4: QS_TILES(4, kTileKeysPrompt); break;
+      case 6: QS_TILES(6, kTileKeysPrompt); break;
+      case 8: QS_TILES(8, kTileKeysPrompt); break;
+      default: QS_TILES(16, 64); break;  // 128 accumulator registers: two blocks per SM either way
     }
 #undef QS_TILES
     if (rc) return rc;
