@@ -829,45 +829,61 @@ __global__ void group_merge_kernel(ST* __restrict__ out, long long out_stride, c
 //   prepared row (fp32): [G*D q | G*D k | H*Dv v | H beta | H decay]
 //   convolution state (fp32): [slots][taps - 1][C], oldest first, C = 2 G D + H Dv
 // ---------------------------------------------------------------------------------------------------------------------------------
+// One block per (token, unit); the units of a token are its G q heads, its G k heads (D channels each, made unit vectors) and its H value
+// heads (Dv channels): single tokens of a small batch still fill the SMs.  Unit 0 also writes the token's write strengths and decays.
+constexpr int kPrepThreads = 128, kPrepPerThread = 8;  // channels of a unit <= 1024
+
 template <typename ST>
-__global__ void delta_prepare_kernel(float* __restrict__ prep, const ST* __restrict__ proj, long long stride, const float* __restrict__ conv_w,
-                                     const float* __restrict__ conv_state, const float* __restrict__ a_log, const float* __restrict__ dt_bias,
-                                     const int* __restrict__ tok_entry, const int* __restrict__ tok_pos, const int* __restrict__ entry_start,
-                                     const int* __restrict__ entry_slot, int H, int G, int D, int Dv, int taps, float unit_eps) {
-  extern __shared__ float y[];  // [C]
-  const int t = blockIdx.x;
+__global__ void __launch_bounds__(kPrepThreads) delta_prepare_kernel(
+    float* __restrict__ prep, const ST* __restrict__ proj, long long stride, const float* __restrict__ conv_w,
+    const float* __restrict__ conv_state, const float* __restrict__ a_log, const float* __restrict__ dt_bias, const int* __restrict__ tok_entry,
+    const int* __restrict__ tok_pos, const int* __restrict__ entry_start, const int* __restrict__ entry_slot, int H, int G, int D, int Dv,
+    int taps, float unit_eps) {
+  __shared__ float red[33];
+  const int t = blockIdx.x, u = blockIdx.y;
   const int C = 2 * G * D + H * Dv;
   const int P = C + 2 * H;
+  const bool qk = u < 2 * G;
+  const int c0 = qk ? u * D : 2 * G * D + (u - 2 * G) * Dv, n = qk ? D : Dv;
   const int e = tok_entry[t], pos = tok_pos[t];
   const int local = t - entry_start[e];
   const float* st = conv_state + (size_t)entry_slot[e] * (taps - 1) * C;
-  for (int c = threadIdx.x; c < C; c += blockDim.x) {
-    float a = 0.f;
-    for (int j = 0; j < taps; ++j) {
-      const int back = taps - 1 - j;
-      if (pos - back < 0) continue;
-      float x;
-      if (local - back >= 0) x = ldf(proj + (size_t)(t - back) * stride + c);
-      else x = st[(size_t)(taps - 1 + local - back) * C + c];
-      a += conv_w[(size_t)c * taps + j] * x;
+  float y[kPrepPerThread];
+  float ss = 0.f;
+#pragma unroll
+  for (int k = 0; k < kPrepPerThread; ++k) {
+    const int i = threadIdx.x + k * kPrepThreads;
+    y[k] = 0.f;
+    if (i < n) {
+      const int c = c0 + i;
+      float a = 0.f;
+      for (int j = 0; j < taps; ++j) {
+        const int back = taps - 1 - j;
+        if (pos - back < 0) continue;
+        float x;
+        if (local - back >= 0) x = ldf(proj + (size_t)(t - back) * stride + c);
+        else x = st[(size_t)(taps - 1 + local - back) * C + c];
+        a += conv_w[(size_t)c * taps + j] * x;
+      }
+      y[k] = silu_f(a);
+      ss += y[k] * y[k];
     }
-    y[c] = silu_f(a);
   }
-  __syncthreads();
-  float* o = prep + (size_t)t * P;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
-  for (int u = warp; u < 2 * G; u += nw) {  // q heads then k heads
-    const float* v = y + (size_t)u * D;
-    float ss = 0.f;
-    for (int i = lane; i < D; i += 32) ss += v[i] * v[i];
-    ss = warp_sum(ss);
-    float r = 1.f / sqrtf(ss + unit_eps);
+  float r = 1.f;
+  if (qk) {  // block-uniform
+    ss = block_sum(ss, red);
+    r = 1.f / sqrtf(ss + unit_eps);
     if (u < G) r *= 1.f / sqrtf((float)D);
-    for (int i = lane; i < D; i += 32) o[(size_t)u * D + i] = v[i] * r;
   }
-  for (int c = 2 * G * D + threadIdx.x; c < C; c += blockDim.x) o[c] = y[c];
+  float* o = prep + (size_t)t * P;
+#pragma unroll
+  for (int k = 0; k < kPrepPerThread; ++k) {
+    const int i = threadIdx.x + k * kPrepThreads;
+    if (i < n) o[c0 + i] = y[k] * r;
+  }
+  if (u != 0) return;
   const ST* row = proj + (size_t)t * stride;
-  for (int hh = threadIdx.x; hh < H; hh += blockDim.x) {
+  for (int hh = threadIdx.x; hh < H; hh += kPrepThreads) {
     const float b = ldf(row + C + H * Dv + hh);
     const float a = ldf(row + C + H * Dv + H + hh) + dt_bias[hh];
     const float sp = a > 20.f ? a : log1pf(expf(a));
@@ -912,26 +928,28 @@ __device__ __forceinline__ float part_sum(float v) {
   return v;
 }
 
-template <int DP, int PARTS, int CH, bool VEC>  // VEC: rows of `prep`, D and Dv are multiples of 4 floats: stage with 16-byte copies
+template <int DP, int PARTS, int CH, int CPT, bool VEC>  // VEC: rows of `prep`, D and Dv are multiples of 4 floats: stage with 16-byte copies
 __global__ void __launch_bounds__(128) delta_scan_kernel(float* __restrict__ o_raw, const float* __restrict__ prep, float* __restrict__ state,
                                                          const int* __restrict__ entry_start, const int* __restrict__ entry_len,
                                                          const int* __restrict__ entry_slot, const int* __restrict__ entry_pos0, int H, int G, int D,
                                                          int Dv) {
   extern __shared__ __align__(16) float sm[];  // [2][CH][ROW]
-  constexpr int Q = DP / PARTS, SEG = Q + 4, COLS = 128 / PARTS;  // a part's q / k segment is padded by 16 bytes: parts hit different banks
+  constexpr int Q = DP / PARTS, SEG = Q + 4, TC = 128 / PARTS, COLS = TC * CPT;  // a part's q / k segment is padded by 16 bytes: parts hit different banks
   constexpr int QK = PARTS * SEG, ROW = 2 * QK + COLS + 4;
   const int e = blockIdx.x, h = blockIdx.y, cg = blockIdx.z, g = h / (H / G);
-  const int tid = threadIdx.x, part = tid % PARTS, cl = tid / PARTS, col = cg * COLS + cl;
+  const int tid = threadIdx.x, part = tid % PARTS, cl = tid / PARTS, col0 = cg * COLS + cl * CPT;  // CPT adjacent columns per thread
   const int C = 2 * G * D + H * Dv, P = C + 2 * H;
   const int n = entry_len[e], s0 = entry_start[e];
-  const bool live = col < Dv, fresh = entry_pos0[e] == 0;
+  const bool fresh = entry_pos0[e] == 0;
   float* Sg = state + ((size_t)entry_slot[e] * H + h) * (size_t)D * Dv;
-  float S[Q];
+  float S[CPT][Q];
 #pragma unroll
-  for (int j = 0; j < Q; ++j) {
-    const int i = part * Q + j;
-    S[j] = (live && !fresh && i < D) ? Sg[(size_t)i * Dv + col] : 0.f;
-  }
+  for (int c = 0; c < CPT; ++c)
+#pragma unroll
+    for (int j = 0; j < Q; ++j) {
+      const int i = part * Q + j;
+      S[c][j] = (col0 + c < Dv && !fresh && i < D) ? Sg[(size_t)i * Dv + col0 + c] : 0.f;
+    }
   auto stage = [&](int chunk, int buf) {
     if (VEC) {
       constexpr int QV = Q / 4, NQK = 2 * PARTS * QV, NV = COLS / 4, ITEMS = NQK + NV + 2;
@@ -1006,38 +1024,54 @@ __global__ void __launch_bounds__(128) delta_scan_kernel(float* __restrict__ o_r
       const float* r = sm + (size_t)((ch & 1) * CH + tk) * ROW;
       const float4* q4 = reinterpret_cast<const float4*>(r + part * SEG);
       const float4* k4 = reinterpret_cast<const float4*>(r + QK + part * SEG);
-      const float v = r[2 * QK + cl], beta = r[2 * QK + COLS], decay = r[2 * QK + COLS + 1];
-      float kp[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      const float beta = r[2 * QK + COLS], decay = r[2 * QK + COLS + 1];
+      // a q / k word read from shared memory serves the thread's CPT columns
+      float kp[CPT][4];
+#pragma unroll
+      for (int c = 0; c < CPT; ++c) kp[c][0] = kp[c][1] = kp[c][2] = kp[c][3] = 0.f;
 #pragma unroll
       for (int j = 0; j < Q / 4; ++j) {
         const float4 kk = k4[j];
-        const int a = (j & 1) * 4;
-        kp[a] += S[4 * j] * kk.x; kp[a + 1] += S[4 * j + 1] * kk.y; kp[a + 2] += S[4 * j + 2] * kk.z; kp[a + 3] += S[4 * j + 3] * kk.w;
+#pragma unroll
+        for (int c = 0; c < CPT; ++c) {
+          kp[c][0] += S[c][4 * j] * kk.x; kp[c][1] += S[c][4 * j + 1] * kk.y; kp[c][2] += S[c][4 * j + 2] * kk.z; kp[c][3] += S[c][4 * j + 3] * kk.w;
+        }
       }
-      const float kS = part_sum<PARTS>(((kp[0] + kp[1]) + (kp[2] + kp[3])) + ((kp[4] + kp[5]) + (kp[6] + kp[7]))) * decay;
-      const float u = beta * (v - kS);
-      float op[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      float u[CPT];
+#pragma unroll
+      for (int c = 0; c < CPT; ++c) {
+        const float kS = part_sum<PARTS>((kp[c][0] + kp[c][1]) + (kp[c][2] + kp[c][3])) * decay;
+        u[c] = beta * (r[2 * QK + cl * CPT + c] - kS);
+      }
+      float op[CPT][4];
+#pragma unroll
+      for (int c = 0; c < CPT; ++c) op[c][0] = op[c][1] = op[c][2] = op[c][3] = 0.f;
 #pragma unroll
       for (int j = 0; j < Q / 4; ++j) {
         const float4 kk = k4[j], qq = q4[j];
-        const int a = (j & 1) * 4;
-        S[4 * j] = S[4 * j] * decay + kk.x * u;         op[a] += S[4 * j] * qq.x;
-        S[4 * j + 1] = S[4 * j + 1] * decay + kk.y * u; op[a + 1] += S[4 * j + 1] * qq.y;
-        S[4 * j + 2] = S[4 * j + 2] * decay + kk.z * u; op[a + 2] += S[4 * j + 2] * qq.z;
-        S[4 * j + 3] = S[4 * j + 3] * decay + kk.w * u; op[a + 3] += S[4 * j + 3] * qq.w;
+#pragma unroll
+        for (int c = 0; c < CPT; ++c) {
+          S[c][4 * j] = S[c][4 * j] * decay + kk.x * u[c];         op[c][0] += S[c][4 * j] * qq.x;
+          S[c][4 * j + 1] = S[c][4 * j + 1] * decay + kk.y * u[c]; op[c][1] += S[c][4 * j + 1] * qq.y;
+          S[c][4 * j + 2] = S[c][4 * j + 2] * decay + kk.z * u[c]; op[c][2] += S[c][4 * j + 2] * qq.z;
+          S[c][4 * j + 3] = S[c][4 * j + 3] * decay + kk.w * u[c]; op[c][3] += S[c][4 * j + 3] * qq.w;
+        }
       }
-      const float o = part_sum<PARTS>(((op[0] + op[1]) + (op[2] + op[3])) + ((op[4] + op[5]) + (op[6] + op[7])));
-      if (part == 0 && live) o_raw[(size_t)(s0 + ch * CH + tk) * H * Dv + (size_t)h * Dv + col] = o;
+#pragma unroll
+      for (int c = 0; c < CPT; ++c) {
+        const float o = part_sum<PARTS>((op[c][0] + op[c][1]) + (op[c][2] + op[c][3]));
+        if (part == 0 && col0 + c < Dv) o_raw[(size_t)(s0 + ch * CH + tk) * H * Dv + (size_t)h * Dv + col0 + c] = o;
+      }
     }
     __syncthreads();
   }
-  if (live) {
+#pragma unroll
+  for (int c = 0; c < CPT; ++c)
 #pragma unroll
     for (int j = 0; j < Q; ++j) {
       const int i = part * Q + j;
-      if (i < D) Sg[(size_t)i * Dv + col] = S[j];
+      if (col0 + c < Dv && i < D) Sg[(size_t)i * Dv + col0 + c] = S[c][j];
     }
-  }
 }
 
 // step 3: per (token, head) unit-RMS read-out times a shared per-dimension weight times silu(output gate); one warp each
@@ -1134,36 +1168,30 @@ int launch_delta(void* out, long long out_stride, float* prep, float* o_raw, con
                  const int* tok_pos, const int* entry_start, const int* entry_len, const int* entry_slot, const int* entry_pos0, int T, int E,
                  int H, int G, int D, int Dv, int taps, float unit_eps, float eps, cudaStream_t s) {
   const int C = 2 * G * D + H * Dv;
-  const size_t smem = (size_t)C * sizeof(float);
-  if (smem > 48 * 1024) cudaFuncSetAttribute(delta_prepare_kernel<ST>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  delta_prepare_kernel<ST><<<T, 256, smem, s>>>(prep, (const ST*)proj, stride, conv_w, conv_state, a_log, dt_bias, tok_entry, tok_pos, entry_start,
-                                                 entry_slot, H, G, D, Dv, taps, unit_eps);
+  delta_prepare_kernel<ST><<<dim3(T, 2 * G + H), kPrepThreads, 0, s>>>(prep, (const ST*)proj, stride, conv_w, conv_state, a_log, dt_bias, tok_entry,
+                                                                      tok_pos, entry_start, entry_slot, H, G, D, Dv, taps, unit_eps);
   if (taps > 1)
     delta_conv_state_kernel<ST><<<dim3((C + 127) / 128, E), 128, 0, s>>>(conv_state, (const ST*)proj, stride, entry_start, entry_len, entry_slot,
                                                                           entry_pos0, C, taps);
   // 16-byte staging needs every q / k / v run of a prepared row on a 16-byte boundary
   const bool vec = D % 4 == 0 && Dv % 4 == 0 && (C + 2 * H) % 4 == 0 && (reinterpret_cast<uintptr_t>(prep) & 15) == 0;
   // rows of a column per thread: all of them up to 64 (a warp then reads q / k as broadcasts), 64 above
-#define QS_SCAN(DP, PARTS, CH)                                                                                                                \
+#define QS_SCAN(DP, PARTS, CH, CPT)                                                                                                           \
   do {                                                                                                                                        \
-    constexpr int cols = 128 / PARTS;                                                                                                         \
+    constexpr int cols = 128 / PARTS * CPT;                                                                                                   \
     const size_t sm = (size_t)2 * CH * (2 * PARTS * (DP / PARTS + 4) + cols + 4) * sizeof(float);                                             \
     dim3 grid(E, H, (Dv + cols - 1) / cols);                                                                                                  \
-    if (vec) {                                                                                                                              \
-      if (sm > 48 * 1024) cudaFuncSetAttribute(delta_scan_kernel<DP, PARTS, CH, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm); \
-      delta_scan_kernel<DP, PARTS, CH, true><<<grid, 128, sm, s>>>(o_raw, prep, state, entry_start, entry_len, entry_slot, entry_pos0, H, G,  \
-                                                                   D, Dv);                                                                    \
-    } else {                                                                                                                                  \
-      if (sm > 48 * 1024) cudaFuncSetAttribute(delta_scan_kernel<DP, PARTS, CH, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);\
-      delta_scan_kernel<DP, PARTS, CH, false><<<grid, 128, sm, s>>>(o_raw, prep, state, entry_start, entry_len, entry_slot, entry_pos0, H, G, \
-                                                                    D, Dv);                                                                   \
-    }                                                                                                                                         \
+    auto kern = vec ? delta_scan_kernel<DP, PARTS, CH, CPT, true> : delta_scan_kernel<DP, PARTS, CH, CPT, false>;                             \
+    if (sm > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);                                     \
+    kern<<<grid, 128, sm, s>>>(o_raw, prep, state, entry_start, entry_len, entry_slot, entry_pos0, H, G, D, Dv);                              \
   } while (0)
-  if (D <= 16) QS_SCAN(16, 1, 16);
-  else if (D <= 32) QS_SCAN(32, 1, 16);
-  else if (D <= 64) QS_SCAN(64, 2, 16);
-  else if (D <= 128) QS_SCAN(128, 4, 16);
-  else QS_SCAN(256, 8, 8);
+  // two adjacent columns per thread where the head has the columns for it: a q / k word read from shared memory then feeds two columns
+  // (the scan is bound by shared-memory bandwidth: every thread reads its rows' q and k for every token)
+  if (D <= 16) QS_SCAN(16, 1, 16, 1);
+  else if (D <= 32) QS_SCAN(32, 1, 16, 1);
+  else if (D <= 64) { if (Dv >= 128) QS_SCAN(64, 2, 16, 2); else QS_SCAN(64, 2, 16, 1); }
+  else if (D <= 128) { if (Dv >= 64) QS_SCAN(128, 8, 16, 2); else QS_SCAN(128, 4, 16, 1); }
+  else QS_SCAN(256, 8, 8, 1);
 #undef QS_SCAN
   const int warps = T * H;
   delta_gate_out_kernel<ST><<<(warps + 3) / 4, 128, 0, s>>>((ST*)out, out_stride, o_raw, (const ST*)proj, stride, norm_w, T, H, G, D, Dv, eps);
