@@ -211,9 +211,9 @@ QS_API int qs_silu_and_mul_quant(int8_t* out, const void* input, void* input_sum
  * --------------------------------------------------------------------------------------------------------- */
 #define QS_DTYPE_BF16 0
 #define QS_DTYPE_F32 1
-/* out[t] = table[tokens[t]] + pair_table[prev[t] < 0 ? buckets : (prev[t] * mul_prev + tokens[t] * mul_cur) % buckets]; pair_table may be NULL */
+/* out[t, c] (c < copies: out is [tokens, copies, width]) = table[tokens[t]] * scale + pair_table[prev[t] < 0 ? buckets : (prev[t] * mul_prev + tokens[t] * mul_cur) % buckets]; pair_table may be NULL */
 QS_API int qs_hyb_embed(float* out, const int32_t* tokens, const int32_t* prev, const void* table, const void* pair_table, int tokens_n,
-                        int width, int buckets, int64_t mul_prev, int64_t mul_cur, int dtype, void* stream);
+                        int width, int buckets, int64_t mul_prev, int64_t mul_cur, float scale, int copies, int dtype, void* stream);
 /* [x <- x + add (storage type, may be NULL);]  out_k = x * rsqrt(mean(x^2) + eps) * (offset + w_k), k = 1, 2 (out2 / w2 may be NULL);
  * x fp32 [tokens, width] (updated in place when add is given), w fp32 */
 QS_API int qs_hyb_rms_norm(void* out1, void* out2, float* x, const void* add, const float* w1, const float* w2, float offset, float eps,
@@ -228,12 +228,15 @@ QS_API int qs_hyb_gelu_tanh_mul(void* out, int64_t out_stride, const void* in, i
 QS_API int qs_hyb_rope_append(void* proj, int64_t stride, const int32_t* tok_slot, const int32_t* tok_pos, const int32_t* block_table,
                               int max_blocks, void* kpool, void* vpool, const float* inv_freq, float amplitude, int tokens_n, int heads,
                               int kv_heads, int maps, int dim, int vdim, int rot_dims, int page_size, int dtype, void* stream);
-/* causal attention of every token over positions 0..tok_pos of its sequence in the paged cache, `maps` (1 or 2) softmax maps per head
- * over shared values: o = a1 [- lambda a2]; head_norm: o *= rsqrt(mean(o^2) + eps); o *= out_scale.  out [tokens, heads*vdim] */
+/* causal attention of every token over positions first..tok_pos of its sequence in the paged cache, `maps` (1 or 2) softmax maps per head
+ * over shared values: o = a1 [- lambda a2]; head_norm: o *= rsqrt(mean(o^2) + eps); o *= out_scale.  out [tokens, heads*vdim].
+ * first = start of the position's chunk of `chunk` positions (0: no chunks; chunks count from position 0 of the sequence), and at least
+ * tok_pos - window + 1 (0: no window).  sinks (fp32 [heads], may be NULL): one more term exp(sinks[head]) in every softmax denominator of
+ * the head, without a value and outside `scale`. */
 QS_API int qs_hyb_attention(void* out, int64_t out_stride, const void* q, int64_t q_stride, const void* kpool, const void* vpool,
                             const int32_t* tok_slot, const int32_t* tok_pos, const int32_t* block_table, int max_blocks, int tokens_n,
                             int heads, int kv_heads, int maps, int dim, int vdim, float scale, float lambda, float out_scale, float eps,
-                            int head_norm, int page_size, int dtype, void* stream);
+                            int head_norm, int page_size, int chunk, int window, const float* sinks, int dtype, void* stream);
 /* The same attention on the fast kernels (bfloat16 storage, dim and vdim multiples of 16, vdim in {32, 64, 96, 128, 256}, heads / kv_heads <= 16):
  * entries of at least 16 tokens run as 64-row tiles on the tensor cores (tile_entry / tile_row0: entry and first row within it of every tile;
  * long_tokens: their token rows), the tokens listed in short_tokens one by one, the query heads of a key/value head as the rows of a
@@ -259,6 +262,49 @@ QS_API int qs_hyb_gated_delta(void* out, int64_t out_stride, float* prep, float*
                               const int32_t* tok_entry, const int32_t* tok_pos, const int32_t* entry_start, const int32_t* entry_len,
                               const int32_t* entry_slot, const int32_t* entry_pos0, int tokens_n, int entries, int heads, int kv_heads,
                               int dim, int vdim, int taps, float unit_eps, float eps, int dtype, void* stream);
+
+/* Residual streams x fp32 [tokens, streams, width] (hyper-connections; streams = 1 with all coefficients 1 is the plain residual).  In order:
+ * (upd != NULL) every stream at once from the old ones: x_t <- sum_s upd_mix[s, t] x_s + upd_out[t] upd (upd: [tokens, width], fp32 if
+ * upd_f32, else storage type);  u = sum_s in_coef[s] x_s (in_coef NULL: the plain sum);  (out_sum != NULL) out_sum <- u (fp32);
+ * (out_h != NULL) out_h <- u brought to unit RMS in `groups` equal consecutive parts, times (offset + w) (storage type; w fp32 [width]). */
+QS_API int qs_hyb_stream_norm(void* out_h, float* out_sum, float* x, int streams, const void* upd, int upd_f32, const float* upd_mix,
+                              const float* upd_out, const float* in_coef, const float* w, int groups, float offset, float eps, int tokens_n,
+                              int width, int dtype, void* stream);
+/* y = scale (a rsqrt(mean(a^2) + eps) wa + b rsqrt(mean(b^2) + eps) wb) per row; a, b storage type [tokens, width], y fp32 */
+QS_API int qs_hyb_branch_norm_mean(float* y, const void* a, const void* b, const float* wa, const float* wb, float scale, float eps, int tokens_n,
+                                   int width, int dtype, void* stream);
+/* Query / key preparation and cache append for one softmax map per head.  Projection rows [H*dim q | G*dim k | G*vdim v]; bias (fp32, same
+ * layout) and q_factor (fp32 [H]) may be NULL.  Per head: + bias; (unit_rms) x *= rsqrt(mean(x^2) + eps); rotary on the first rot_dims
+ * entries (rot_layout 0: pairs (2i, 2i+1); 1: pairs (i, i + rot_dims/2); angle = position * inv_freq[i]; rot_dims 0: none); queries times
+ * q_factor[head], in place.  Keys and values (+ bias) go to the pages K [page][page_size][G][dim], V [page][page_size][G][vdim]. */
+QS_API int qs_hyb_qk_prepare_append(void* proj, int64_t stride, const float* bias, const float* q_factor, const int32_t* tok_slot,
+                                    const int32_t* tok_pos, const int32_t* block_table, int max_blocks, void* kpool, void* vpool,
+                                    const float* inv_freq, int rot_layout, int rot_dims, int unit_rms, float eps, int tokens_n, int heads,
+                                    int kv_heads, int dim, int vdim, int page_size, int dtype, void* stream);
+/* Gate recurrence (HGRN2) over projection rows [H*dim q | H*dim f | H*vdim v]: q <- silu(q), f <- lower + (1 - lower) sigmoid(f + f_bias)
+ * (fp32 [H*dim] each), per head S <- diag(f) S + (1 - f) v^T, o = S^T q, out = o rsqrt(mean(o^2) + eps) norm_w (fp32 [vdim], may be NULL).
+ * state fp32 [slots, H, dim, vdim]; a run that starts at position 0 starts from zero.  prep fp32 [tokens, 2 H dim + H vdim] and o_raw fp32
+ * [tokens, H vdim] are scratch. */
+QS_API int qs_hyb_gate_recurrence(void* out, int64_t out_stride, float* prep, float* o_raw, const void* proj, int64_t stride, const float* f_bias,
+                                  const float* lower, const float* norm_w, float* state, const int32_t* entry_start, const int32_t* entry_len,
+                                  const int32_t* entry_slot, const int32_t* entry_pos0, int tokens_n, int entries, int heads, int dim, int vdim,
+                                  float eps, int dtype, void* stream);
+/* Retention over projection rows [H*dim q | H*dim k | H*vdim v | H*vdim gate]: q and k rotated on their first rot_dims entries (entry i
+ * paired with i + rot_dims/2, angle = position * inv_freq[i]), k times k_scale, per head S <- head_decay[h] S + k v^T, o = S^T q,
+ * out = o rsqrt(mean(o^2) + eps) [silu(gate) if gated].  state, prep and o_raw as for the gate recurrence. */
+QS_API int qs_hyb_retention(void* out, int64_t out_stride, float* prep, float* o_raw, const void* proj, int64_t stride, const float* head_decay,
+                            const float* inv_freq, int rot_dims, float k_scale, int gated, float* state, const int32_t* tok_pos,
+                            const int32_t* entry_start, const int32_t* entry_len, const int32_t* entry_slot, const int32_t* entry_pos0,
+                            int tokens_n, int entries, int heads, int dim, int vdim, float eps, int dtype, void* stream);
+/* Mixture-of-experts router: fp32 logits w_router [experts, width] h, softmax over all experts, the `top` largest scores kept as they are.
+ * route fp32 [tokens, experts] (score of a chosen expert, 0 elsewhere), top_idx int32 / top_w fp32 [tokens, top], best first. */
+QS_API int qs_hyb_moe_router(float* route, int32_t* top_idx, float* top_w, const void* h, const float* w_router, int tokens_n, int width,
+                             int experts, int top, int dtype, void* stream);
+/* Activation of all experts' columns of a token: in rows [F gate | F up], F = experts * ff + ff_shared (the shared expert's columns last);
+ * g = min(gate, limit), u = clamp(up, -limit, limit), out = route[t, expert] g sigmoid(alpha g) (u + 1); shared columns: weight 1 and
+ * limit_shared.  out [tokens, F]. */
+QS_API int qs_hyb_moe_act(void* out, const void* in, const float* route, int tokens_n, int experts, int ff, float limit, int ff_shared,
+                          float limit_shared, float alpha, int dtype, void* stream);
 
 #ifdef __cplusplus
 }

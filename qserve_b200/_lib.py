@@ -51,17 +51,25 @@ SIGNATURES = {
     "qs_gelu_fast": (c_int, [_P, _P, _I, _I, _P]),
     "qs_dequant_silu_and_mul_quant": (c_int, [_P, _P, _F, _F, _F, _P, _P, _I, _I, _P]),
     # unquantised hybrid decoders (csrc/hybrid.cu)
-    "qs_hyb_embed": (c_int, [_P, _P, _P, _P, _P, _I, _I, _I, _L, _L, _I, _P]),
+    "qs_hyb_embed": (c_int, [_P, _P, _P, _P, _P, _I, _I, _I, _L, _L, _F, _I, _I, _P]),
     "qs_hyb_rms_norm": (c_int, [_P, _P, _P, _P, _P, _P, _F, _F, _I, _I, _I, _P]),
     "qs_hyb_residual_add": (c_int, [_P, _P, _L, _I, _P]),
     "qs_hyb_gelu_tanh_mul": (c_int, [_P, _L, _P, _I, _I, _I, _P]),
     "qs_hyb_rope_append": (c_int, [_P, _L, _P, _P, _P, _I, _P, _P, _P, _F, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P]),
-    "qs_hyb_attention": (c_int, [_P, _L, _P, _L, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _F, _F, _F, _I, _I, _I, _P]),
+    "qs_hyb_attention": (c_int, [_P, _L, _P, _L, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _F, _F, _F, _I, _I, _I, _I, _P, _I, _P]),
     "qs_hyb_attention_fast_supported": (c_int, [_I, _I, _I, _I, _I, _I, _L]),
     "qs_hyb_attention_scratch_floats": (_L, [_I, _I, _I, _I, _I]),
     "qs_hyb_attention_fast": (c_int, [_P, _L, _P, _L, _P, _P, _P, _P, _P, _I, _P, _P, _I, _P, _I, _P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I,
                                       _F, _F, _F, _F, _I, _I, _I, _P]),
     "qs_hyb_gated_delta": (c_int, [_P, _L, _P, _P, _P, _L, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _F, _I, _P]),
+    # csrc/hybrid_blocks.cu, csrc/hybrid_linear.cu
+    "qs_hyb_stream_norm": (c_int, [_P, _P, _P, _I, _P, _I, _P, _P, _P, _P, _I, _F, _F, _I, _I, _I, _P]),
+    "qs_hyb_branch_norm_mean": (c_int, [_P, _P, _P, _P, _P, _F, _F, _I, _I, _I, _P]),
+    "qs_hyb_qk_prepare_append": (c_int, [_P, _L, _P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _F, _I, _I, _I, _I, _I, _I, _I, _P]),
+    "qs_hyb_gate_recurrence": (c_int, [_P, _L, _P, _P, _P, _L, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P]),
+    "qs_hyb_retention": (c_int, [_P, _L, _P, _P, _P, _L, _P, _P, _I, _F, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P]),
+    "qs_hyb_moe_router": (c_int, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P]),
+    "qs_hyb_moe_act": (c_int, [_P, _P, _P, _I, _I, _I, _F, _I, _F, _F, _I, _P]),
 }
 
 ABI_VERSION = 1

@@ -14,7 +14,8 @@ from typing import Dict, List
 
 import torch
 
-from .modelcfg import AttentionMixerConfig, DeltaMixerConfig, HybridConfig
+from .modelcfg import (AttentionMixerConfig, DeltaMixerConfig, GateRecurrenceMixerConfig, HybridConfig, ParallelMixerConfig,
+                       RetentionMixerConfig)
 
 
 class OutOfPages(RuntimeError):
@@ -64,22 +65,24 @@ class HybridCache:
         self.block_table = torch.zeros((max_seqs, self.max_blocks), dtype=torch.int32, device=device)
         self._table_dirty = True
         # per layer RUN (a looped layer has one cache / state per pass)
-        self.runs = []
-        for li in cfg.schedule():
-            m = cfg.layers[li].mixer
-            if isinstance(m, AttentionMixerConfig):
-                self.runs.append({
-                    "k": torch.zeros((self.num_pages, page_size, m.kv_heads, m.maps * m.dim), dtype=dtype, device=device),
-                    "v": torch.zeros((self.num_pages, page_size, m.kv_heads, m.vdim), dtype=dtype, device=device),
-                })
-            elif isinstance(m, DeltaMixerConfig):
-                c = 2 * m.kv_heads * m.dim + m.heads * m.vdim
-                self.runs.append({
-                    "state": torch.zeros((max_seqs, m.heads, m.dim, m.vdim), dtype=torch.float32, device=device),
-                    "conv": torch.zeros((max_seqs, max(m.conv - 1, 1), c), dtype=torch.float32, device=device),
-                })
-            else:
-                raise TypeError(type(m))
+        self.runs = [self.mixer_storage(cfg.layers[li].mixer) for li in cfg.schedule()]
+
+    def mixer_storage(self, m) -> dict:
+        """What one run of a mixer keeps between steps: pages for an attention layer, a slot-indexed fp32 state for a recurrent one, both
+        (under "left" / "right") for two mixers side by side."""
+        dtype, device, page_size, max_seqs = self.dtype, self.device, self.page_size, self.max_seqs
+        if isinstance(m, AttentionMixerConfig):
+            return {"k": torch.zeros((self.num_pages, page_size, m.kv_heads, m.maps * m.dim), dtype=dtype, device=device),
+                    "v": torch.zeros((self.num_pages, page_size, m.kv_heads, m.vdim), dtype=dtype, device=device)}
+        if isinstance(m, DeltaMixerConfig):
+            c = 2 * m.kv_heads * m.dim + m.heads * m.vdim
+            return {"state": torch.zeros((max_seqs, m.heads, m.dim, m.vdim), dtype=torch.float32, device=device),
+                    "conv": torch.zeros((max_seqs, max(m.conv - 1, 1), c), dtype=torch.float32, device=device)}
+        if isinstance(m, (GateRecurrenceMixerConfig, RetentionMixerConfig)):
+            return {"state": torch.zeros((max_seqs, m.heads, m.dim, m.vdim), dtype=torch.float32, device=device)}
+        if isinstance(m, ParallelMixerConfig):
+            return {"left": self.mixer_storage(m.left), "right": self.mixer_storage(m.right)}
+        raise TypeError(type(m))
 
     # ----------------------------------------------------------------------------------------------------------------
     def admit(self, seq_id) -> SequenceState:

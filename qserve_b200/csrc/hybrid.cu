@@ -15,56 +15,21 @@
 
 #include "../../include/qserve_b200.h"
 #include "common.cuh"
+#include "hybrid_common.cuh"
 #include "launch.h"
 
 namespace qs {
 namespace {
 
-template <typename ST> __device__ __forceinline__ float ldf(const ST* p);
-template <> __device__ __forceinline__ float ldf<float>(const float* p) { return *p; }
-template <> __device__ __forceinline__ float ldf<__nv_bfloat16>(const __nv_bfloat16* p) { return __bfloat162float(*p); }
-template <typename ST> __device__ __forceinline__ void stf(ST* p, float v);
-template <> __device__ __forceinline__ void stf<float>(float* p, float v) { *p = v; }
-template <> __device__ __forceinline__ void stf<__nv_bfloat16>(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
+using namespace hyb;
 
-__device__ __forceinline__ float warp_sum(float v) {
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-  return v;
-}
-__device__ __forceinline__ float warp_max(float v) {
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
-  return v;
-}
-// block-wide sum / max over up to 32 warps; `red` holds 33 floats; every thread gets the result
-__device__ __forceinline__ float block_sum(float v, float* red) {
-  v = warp_sum(v);
-  const int w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
-  __syncthreads();
-  if ((threadIdx.x & 31) == 0) red[w] = v;
-  __syncthreads();
-  float t = (threadIdx.x & 31) < nw ? red[threadIdx.x & 31] : 0.f;
-  return warp_sum(t);
-}
-__device__ __forceinline__ float block_max(float v, float* red) {
-  v = warp_max(v);
-  const int w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
-  __syncthreads();
-  if ((threadIdx.x & 31) == 0) red[w] = v;
-  __syncthreads();
-  float t = (threadIdx.x & 31) < nw ? red[threadIdx.x & 31] : -INFINITY;
-  return warp_max(t);
-}
-
-__device__ __forceinline__ float silu_f(float z) { return z / (1.f + expf(-z)); }
 
 // ---------------------------------------------------------------------------------------------------------------------------------
-// embedding: token row (+ hashed (previous, current) pair row) -> fp32 residual stream
+// embedding: token row times `scale` (+ hashed (previous, current) pair row) -> fp32 residual stream
 // ---------------------------------------------------------------------------------------------------------------------------------
 template <typename ST>
 __global__ void embed_pair_kernel(float* __restrict__ out, const int* __restrict__ tokens, const int* __restrict__ prev, const ST* __restrict__ table,
-                                  const ST* __restrict__ pair, int W, int buckets, long long mul_prev, long long mul_cur) {
+                                  const ST* __restrict__ pair, int W, int buckets, long long mul_prev, long long mul_cur, float scale, int copies) {
   const int t = blockIdx.x;
   const long long tok = tokens[t];
   const ST* e = table + tok * W;
@@ -74,7 +39,10 @@ __global__ void embed_pair_kernel(float* __restrict__ out, const int* __restrict
     const long long row = p < 0 ? buckets : (p * mul_prev + tok * mul_cur) % buckets;
     b = pair + row * W;
   }
-  for (int i = threadIdx.x; i < W; i += blockDim.x) out[(size_t)t * W + i] = ldf(e + i) + (b ? ldf(b + i) : 0.f);
+  for (int i = threadIdx.x; i < W; i += blockDim.x) {
+    const float v = ldf(e + i) * scale + (b ? ldf(b + i) : 0.f);
+    for (int c = 0; c < copies; ++c) out[((size_t)t * copies + c) * W + i] = v;  // every residual stream starts from the embedding
+  }
 }
 
 // ---------------------------------------------------------------------------------------------------------------------------------
@@ -104,19 +72,6 @@ __global__ void rms_norm2_kernel(ST* __restrict__ out1, ST* __restrict__ out2, f
   }
 }
 
-// four elements of the storage type at once
-template <typename ST> __device__ __forceinline__ float4 ld4(const ST* p);
-template <> __device__ __forceinline__ float4 ld4<float>(const float* p) { return *reinterpret_cast<const float4*>(p); }
-template <> __device__ __forceinline__ float4 ld4<__nv_bfloat16>(const __nv_bfloat16* p) {
-  const uint2 u = *reinterpret_cast<const uint2*>(p);
-  return make_float4(__uint_as_float(u.x << 16), __uint_as_float(u.x & 0xffff0000u), __uint_as_float(u.y << 16), __uint_as_float(u.y & 0xffff0000u));
-}
-template <typename ST> __device__ __forceinline__ void st4(ST* p, float4 v);
-template <> __device__ __forceinline__ void st4<float>(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
-template <> __device__ __forceinline__ void st4<__nv_bfloat16>(__nv_bfloat16* p, float4 v) {
-  __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
-  *reinterpret_cast<uint2*>(p) = make_uint2(*reinterpret_cast<uint32_t*>(&a), *reinterpret_cast<uint32_t*>(&b));
-}
 
 // the same norm for widths that are multiples of 4: 16-byte accesses to the stream and the gains, 8- or 16-byte ones to the outputs
 template <typename ST>
@@ -246,6 +201,14 @@ __global__ void rope_append_kernel(ST* __restrict__ proj, long long stride, cons
 // d, d + blockDim, ... for every map.  Epilogue:
 //   MAPS == 2: o = a1 - lambda a2;   then (head_norm) o <- o * rsqrt(mean(o^2) + eps);   o <- o * out_scale
 // ---------------------------------------------------------------------------------------------------------------------------------
+// first position a query at `pos` sees: the start of its chunk of `chunk` positions (0: no chunks), and not further back than `window`
+// positions including its own (0: no window)
+__host__ __device__ __forceinline__ int first_key(int pos, int chunk, int window) {
+  int f = chunk > 0 ? pos - pos % chunk : 0;
+  if (window > 0) f = max(f, pos - window + 1);
+  return f;
+}
+
 constexpr int kAttnThreads = 128;
 constexpr int kAttnKT = 128;
 constexpr int kAttnMaxV = 4;  // value dims per thread: Dv <= 512
@@ -254,7 +217,8 @@ template <typename ST, int MAPS>
 __global__ void __launch_bounds__(kAttnThreads) paged_multimap_attention_kernel(
     ST* __restrict__ out, long long out_stride, const ST* __restrict__ q, long long q_stride, const ST* __restrict__ kpool,
     const ST* __restrict__ vpool, const int* __restrict__ tok_slot, const int* __restrict__ tok_pos, const int* __restrict__ block_table,
-    int max_blocks, int H, int G, int D, int Dv, float scale, float lambda, float out_scale, float eps, int head_norm, int page) {
+    int max_blocks, int H, int G, int D, int Dv, float scale, float lambda, float out_scale, float eps, int head_norm, int page, int chunk,
+    int window, const float* __restrict__ sinks) {
   extern __shared__ float sm[];
   float* qs = sm;                      // [MAPS * D]
   float* ps = qs + MAPS * D;           // [MAPS][KT]
@@ -272,13 +236,14 @@ __global__ void __launch_bounds__(kAttnThreads) paged_multimap_attention_kernel(
   float m_run[MAPS], l_run[MAPS], acc[MAPS][kAttnMaxV];
 #pragma unroll
   for (int m = 0; m < MAPS; ++m) {
-    m_run[m] = -INFINITY;
-    l_run[m] = 0.f;
+    // a sink is one more term exp(sink) of the denominator that carries no value: the running maximum and sum start from it
+    m_run[m] = sinks != nullptr ? sinks[h] : -INFINITY;
+    l_run[m] = sinks != nullptr ? 1.f : 0.f;
 #pragma unroll
     for (int j = 0; j < kAttnMaxV; ++j) acc[m][j] = 0.f;
   }
   const int n_keys = pos + 1;
-  for (int base = 0; base < n_keys; base += kAttnKT) {
+  for (int base = first_key(pos, chunk, window); base < n_keys; base += kAttnKT) {
     const int nk = min(kAttnKT, n_keys - base);
     __syncthreads();  // previous tile's ps / pages fully consumed (and qs written, first time)
     for (int j = threadIdx.x; j < nk; j += blockDim.x) pages[j] = bt[(base + j) / page];
@@ -380,9 +345,6 @@ __device__ __forceinline__ void ldsm_x4_trans(uint32_t (&r)[4], const void* p) {
 __device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
   asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
-__device__ __forceinline__ void cp_async16(void* dst, const void* src) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
 }
 // 2^x on the special-function unit (relative error about 2^-22; -inf gives 0): the bfloat16 kernels' softmax runs in the base-2 domain
 __device__ __forceinline__ float fast_exp2(float x) {
@@ -918,9 +880,6 @@ __global__ void delta_conv_state_kernel(float* __restrict__ conv_state, const ST
 // broadcast).  Tokens are staged CH at a time (q | k | v of the block's columns | beta | decay) with cp.async into a double buffer, so that no
 // global load sits on the token-to-token dependency chain.  Per token, in this order:
 //   S <- decay S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q.
-__device__ __forceinline__ void cp_async4(float* dst, const float* src) {
-  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
-}
 template <int PARTS>
 __device__ __forceinline__ float part_sum(float v) {
 #pragma unroll
@@ -1094,17 +1053,18 @@ __global__ void delta_gate_out_kernel(ST* __restrict__ out, long long out_stride
 template <typename ST>
 int launch_attention(void* out, long long out_stride, const void* q, long long q_stride, const void* kpool, const void* vpool, const int* tok_slot,
                      const int* tok_pos, const int* block_table, int max_blocks, int T, int H, int G, int maps, int D, int Dv, float scale,
-                     float lambda, float out_scale, float eps, int head_norm, int page, cudaStream_t s) {
+                     float lambda, float out_scale, float eps, int head_norm, int page, int chunk, int window, const float* sinks,
+                     cudaStream_t s) {
   const size_t smem = (size_t)(maps * D + maps * kAttnKT + 33) * sizeof(float);
   dim3 grid(T, H);
   if (maps == 2) {
     if (smem > 48 * 1024) cudaFuncSetAttribute(paged_multimap_attention_kernel<ST, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     paged_multimap_attention_kernel<ST, 2><<<grid, kAttnThreads, smem, s>>>((ST*)out, out_stride, (const ST*)q, q_stride, (const ST*)kpool,
-        (const ST*)vpool, tok_slot, tok_pos, block_table, max_blocks, H, G, D, Dv, scale, lambda, out_scale, eps, head_norm, page);
+        (const ST*)vpool, tok_slot, tok_pos, block_table, max_blocks, H, G, D, Dv, scale, lambda, out_scale, eps, head_norm, page, chunk, window, sinks);
   } else {
     if (smem > 48 * 1024) cudaFuncSetAttribute(paged_multimap_attention_kernel<ST, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     paged_multimap_attention_kernel<ST, 1><<<grid, kAttnThreads, smem, s>>>((ST*)out, out_stride, (const ST*)q, q_stride, (const ST*)kpool,
-        (const ST*)vpool, tok_slot, tok_pos, block_table, max_blocks, H, G, D, Dv, scale, lambda, out_scale, eps, head_norm, page);
+        (const ST*)vpool, tok_slot, tok_pos, block_table, max_blocks, H, G, D, Dv, scale, lambda, out_scale, eps, head_norm, page, chunk, window, sinks);
   }
   return check_cuda(cudaGetLastError(), "hyb_attention");
 }
@@ -1213,16 +1173,16 @@ using namespace qs;
 extern "C" {
 
 int qs_hyb_embed(float* out, const int32_t* tokens, const int32_t* prev, const void* table, const void* pair_table, int tokens_n, int width,
-                 int buckets, int64_t mul_prev, int64_t mul_cur, int dtype, void* stream) {
-  QS_REQUIRE(out && tokens && table, "hyb_embed: null tensor");
+                 int buckets, int64_t mul_prev, int64_t mul_cur, float scale, int copies, int dtype, void* stream) {
+  QS_REQUIRE(out && tokens && table && copies >= 1, "hyb_embed: null tensor or no copies");
   QS_REQUIRE(pair_table == nullptr || (prev != nullptr && buckets > 0), "hyb_embed: the pair table needs previous tokens and buckets > 0");
   if (tokens_n == 0) return qs::QS_OK;
   cudaStream_t s = (cudaStream_t)stream;
   QS_DT(dtype,
         (embed_pair_kernel<__nv_bfloat16><<<tokens_n, 128, 0, s>>>(out, tokens, prev, (const __nv_bfloat16*)table, (const __nv_bfloat16*)pair_table,
-                                                                    width, buckets, mul_prev, mul_cur)),
+                                                                    width, buckets, mul_prev, mul_cur, scale, copies)),
         (embed_pair_kernel<float><<<tokens_n, 128, 0, s>>>(out, tokens, prev, (const float*)table, (const float*)pair_table, width, buckets,
-                                                           mul_prev, mul_cur)));
+                                                           mul_prev, mul_cur, scale, copies)));
   return check_cuda(cudaGetLastError(), "hyb_embed");
 }
 
@@ -1292,17 +1252,18 @@ int qs_hyb_rope_append(void* proj, int64_t stride, const int32_t* tok_slot, cons
 int qs_hyb_attention(void* out, int64_t out_stride, const void* q, int64_t q_stride, const void* kpool, const void* vpool,
                      const int32_t* tok_slot, const int32_t* tok_pos, const int32_t* block_table, int max_blocks, int tokens_n, int heads,
                      int kv_heads, int maps, int dim, int vdim, float scale, float lambda, float out_scale, float eps, int head_norm,
-                     int page_size, int dtype, void* stream) {
+                     int page_size, int chunk, int window, const float* sinks, int dtype, void* stream) {
   QS_REQUIRE(out && q && kpool && vpool && tok_slot && tok_pos && block_table, "hyb_attention: null tensor");
+  QS_REQUIRE(chunk >= 0 && window >= 0, "hyb_attention: negative chunk or window");
   QS_REQUIRE(maps == 1 || maps == 2, "hyb_attention: 1 or 2 softmax maps per head");
   QS_REQUIRE(heads % kv_heads == 0 && vdim <= kAttnThreads * kAttnMaxV && page_size > 0, "hyb_attention: bad head geometry (vdim <= 512)");
   if (tokens_n == 0) return qs::QS_OK;
   cudaStream_t s = (cudaStream_t)stream;
   QS_DT(dtype,
         return launch_attention<__nv_bfloat16>(out, out_stride, q, q_stride, kpool, vpool, tok_slot, tok_pos, block_table, max_blocks, tokens_n,
-                                               heads, kv_heads, maps, dim, vdim, scale, lambda, out_scale, eps, head_norm, page_size, s),
+                                               heads, kv_heads, maps, dim, vdim, scale, lambda, out_scale, eps, head_norm, page_size, chunk, window, sinks, s),
         return launch_attention<float>(out, out_stride, q, q_stride, kpool, vpool, tok_slot, tok_pos, block_table, max_blocks, tokens_n, heads,
-                                       kv_heads, maps, dim, vdim, scale, lambda, out_scale, eps, head_norm, page_size, s));
+                                       kv_heads, maps, dim, vdim, scale, lambda, out_scale, eps, head_norm, page_size, chunk, window, sinks, s));
 }
 
 int qs_hyb_attention_fast_supported(int dtype, int heads, int kv_heads, int maps, int dim, int vdim, int64_t q_stride) {

@@ -1,0 +1,367 @@
+// qserve_b200 -- building blocks of the hybrid decoders around the mixers: several residual streams with learned read / write / mixing
+// coefficients (hyper-connections) and a group-wise RMS norm, the mean of two normed branches, query / key preparation with biases and
+// unit-RMS heads, and the router and activation of a mixture-of-experts feed-forward.  The flat token batch is described in hybrid.cu.
+#include <cuda_bf16.h>
+#include <math.h>
+
+#include <algorithm>
+
+#include "../../include/qserve_b200.h"
+#include "common.cuh"
+#include "hybrid_common.cuh"
+#include "launch.h"
+
+namespace qs {
+namespace {
+
+using namespace hyb;
+
+constexpr int kMaxStreams = 8;
+
+// ---------------------------------------------------------------------------------------------------------------------------------
+// Residual streams x [tokens][S][W] fp32.  One block per token:
+//   1. (upd != null) the pending write of the previous sublayer, all streams at once from the old ones:
+//        x_t <- sum_s mix[s][t] x_s + cout[t] y          (y: the sublayer's output row, fp32 or storage type)
+//   2. u = sum_s cin[s] x_s                              (cin == null: the plain sum)
+//   3. (out_sum != null) out_sum <- u   (fp32)
+//   4. (out_h != null) out_h <- u, brought to unit RMS in `groups` equal consecutive parts, times (offset + w)
+// With S = 1, mix = cout = cin = {1} this is the usual residual add followed by a norm.
+// ---------------------------------------------------------------------------------------------------------------------------------
+template <typename ST>
+__global__ void stream_norm_kernel(ST* __restrict__ out_h, float* __restrict__ out_sum, float* __restrict__ x, int S, const void* __restrict__ upd,
+                                   int upd_f32, const float* __restrict__ mix, const float* __restrict__ cout, const float* __restrict__ cin,
+                                   const float* __restrict__ w, int groups, float offset, float eps, int W) {
+  extern __shared__ float dyn[];  // u [W] | partial sums [groups * per] | 1 / rms [groups]
+  __shared__ float c_mix[kMaxStreams * kMaxStreams], c_out[kMaxStreams], c_in[kMaxStreams];
+  const int t = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nw = blockDim.x >> 5;
+  if (tid < S * S) c_mix[tid] = upd != nullptr ? mix[tid] : 0.f;
+  if (tid < S) {
+    c_out[tid] = upd != nullptr ? cout[tid] : 0.f;
+    c_in[tid] = cin != nullptr ? cin[tid] : 1.f;
+  }
+  __syncthreads();
+  float* u_s = dyn;
+  float* xr = x + (size_t)t * S * W;
+  for (int i = tid; i < W; i += blockDim.x) {
+    float xs[kMaxStreams];
+#pragma unroll
+    for (int s = 0; s < kMaxStreams; ++s) xs[s] = s < S ? xr[(size_t)s * W + i] : 0.f;
+    if (upd != nullptr) {
+      const float y = upd_f32 ? static_cast<const float*>(upd)[(size_t)t * W + i] : ldf(static_cast<const ST*>(upd) + (size_t)t * W + i);
+      float nx[kMaxStreams];
+#pragma unroll
+      for (int d = 0; d < kMaxStreams; ++d) {
+        if (d < S) {
+          float a = 0.f;
+#pragma unroll
+          for (int s = 0; s < kMaxStreams; ++s)
+            if (s < S) a += c_mix[s * S + d] * xs[s];
+          nx[d] = a + c_out[d] * y;
+        }
+      }
+#pragma unroll
+      for (int d = 0; d < kMaxStreams; ++d)
+        if (d < S) {
+          xs[d] = nx[d];
+          xr[(size_t)d * W + i] = nx[d];
+        }
+    }
+    float u = 0.f;
+#pragma unroll
+    for (int s = 0; s < kMaxStreams; ++s)
+      if (s < S) u += c_in[s] * xs[s];
+    u_s[i] = u;
+    if (out_sum != nullptr) out_sum[(size_t)t * W + i] = u;
+  }
+  if (out_h == nullptr) return;
+  __syncthreads();
+  // sums of squares: `per` warps share a group, each over its own slice; the slices' sums are added in a fixed order
+  const int part = W / groups, per = max(1, nw / groups), units = groups * per, len = (part + per - 1) / per;
+  float* partial = dyn + W;
+  float* rinv = partial + units;
+  for (int un = warp; un < units; un += nw) {
+    const int g = un / per, sub = un - g * per;
+    const int lo = sub * len, hi = min(part, lo + len);
+    float ss = 0.f;
+    for (int i = lo + lane; i < hi; i += 32) {
+      const float v = u_s[g * part + i];
+      ss += v * v;
+    }
+    ss = warp_sum(ss);
+    if (lane == 0) partial[un] = ss;
+  }
+  __syncthreads();
+  for (int g = tid; g < groups; g += blockDim.x) {
+    float ss = 0.f;
+    for (int sub = 0; sub < per; ++sub) ss += partial[g * per + sub];
+    rinv[g] = 1.f / sqrtf(ss / (float)part + eps);
+  }
+  __syncthreads();
+  for (int i = tid; i < W; i += blockDim.x) stf(out_h + (size_t)t * W + i, u_s[i] * rinv[i / part] * (offset + w[i]));
+}
+
+// y = scale * (a * rsqrt(mean(a^2) + eps) * wa + b * rsqrt(mean(b^2) + eps) * wb): two branches, each normed over the whole row with its own
+// gain; y fp32
+template <typename ST>
+__global__ void branch_norm_mean_kernel(float* __restrict__ y, const ST* __restrict__ a, const ST* __restrict__ b, const float* __restrict__ wa,
+                                        const float* __restrict__ wb, float scale, float eps, int W) {
+  __shared__ float red[33];
+  const size_t base = (size_t)blockIdx.x * W;
+  float sa = 0.f, sb = 0.f;
+  for (int i = threadIdx.x; i < W; i += blockDim.x) {
+    const float va = ldf(a + base + i), vb = ldf(b + base + i);
+    sa += va * va;
+    sb += vb * vb;
+  }
+  sa = block_sum(sa, red);
+  sb = block_sum(sb, red);
+  const float ra = 1.f / sqrtf(sa / (float)W + eps), rb = 1.f / sqrtf(sb / (float)W + eps);
+  for (int i = threadIdx.x; i < W; i += blockDim.x) y[base + i] = scale * (ldf(a + base + i) * ra * wa[i] + ldf(b + base + i) * rb * wb[i]);
+}
+
+// ---------------------------------------------------------------------------------------------------------------------------------
+// Query / key preparation of an attention layer and the append to the paged cache (one softmax map per head).
+//   projection row: [H*D q | G*D k | G*Dv v];  bias (fp32, same layout) may be null
+//   per head, in this order: + bias;  (unit_rms) x <- x * rsqrt(mean(x^2) + eps);  rotary on the first rot_dims entries (layout 0: pairs
+//   (2i, 2i+1), layout 1: pairs (i, i + rot_dims/2); angle = position * inv_freq[i]);  queries times q_factor[head] (may be null)
+// grid (tokens, H + G): the first H blocks finish a query head in place, the others store a key head and its value head (+ bias) in the pages
+// K [page][page_size][G][D], V [page][page_size][G][Dv].
+// ---------------------------------------------------------------------------------------------------------------------------------
+template <typename ST>
+__global__ void qk_prepare_append_kernel(ST* __restrict__ proj, long long stride, const float* __restrict__ bias, const float* __restrict__ q_factor,
+                                         const int* __restrict__ tok_slot, const int* __restrict__ tok_pos, const int* __restrict__ block_table,
+                                         int max_blocks, ST* __restrict__ kpool, ST* __restrict__ vpool, const float* __restrict__ inv_freq,
+                                         int rot_layout, int rot_dims, int unit_rms, float eps, int H, int G, int D, int Dv, int page) {
+  extern __shared__ float hs[];  // the head, D floats
+  __shared__ float red[33];
+  const int t = blockIdx.x, u = blockIdx.y;
+  const int pos = tok_pos[t];
+  ST* row = proj + (size_t)t * stride;
+  const bool is_q = u < H;
+  const int g = u - H;
+  const size_t c0 = is_q ? (size_t)u * D : (size_t)H * D + (size_t)g * D;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < D; i += blockDim.x) {
+    const float v = ldf(row + c0 + i) + (bias != nullptr ? bias[c0 + i] : 0.f);
+    hs[i] = v;
+    ss += v * v;
+  }
+  float r = 1.f;
+  if (unit_rms) {
+    ss = block_sum(ss, red);
+    r = 1.f / sqrtf(ss / (float)D + eps);
+  } else {
+    __syncthreads();
+  }
+  const float f = is_q && q_factor != nullptr ? q_factor[u] : 1.f;
+  ST* dst = row + c0;
+  if (!is_q) {
+    const int pg = block_table[(size_t)tok_slot[t] * max_blocks + pos / page];
+    const size_t cell = (size_t)pg * page + (pos % page);
+    dst = kpool + (cell * G + g) * (size_t)D;
+    const size_t v0 = (size_t)(H + G) * D + (size_t)g * Dv;
+    ST* vd = vpool + (cell * G + g) * (size_t)Dv;
+    for (int i = threadIdx.x; i < Dv; i += blockDim.x) stf(vd + i, ldf(row + v0 + i) + (bias != nullptr ? bias[v0 + i] : 0.f));
+  }
+  const int half = rot_dims >> 1;
+  for (int i = threadIdx.x; i < D; i += blockDim.x) {
+    float v = hs[i] * r;
+    if (i < rot_dims) {
+      int p, other;
+      bool first;
+      if (rot_layout == 0) { p = i >> 1; first = (i & 1) == 0; other = i ^ 1; }
+      else { first = i < half; p = first ? i : i - half; other = first ? i + half : i - half; }
+      float sn, cs;
+      sincosf((float)pos * inv_freq[p], &sn, &cs);
+      const float o = hs[other] * r;
+      v = first ? v * cs - o * sn : v * cs + o * sn;
+    }
+    stf(dst + i, v * f);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------------------------------
+// Router of a mixture of experts: fp32 logits z = W_r h, scores = softmax(z) over all experts, the `top` largest scores are kept (ties: the
+// lower index) as they are (no renormalisation).  One block per token; a warp per expert for the dot products.
+//   route [tokens][E] fp32: the score of a chosen expert, 0 elsewhere;   top_idx / top_w [tokens][top]: the chosen experts, best first
+// ---------------------------------------------------------------------------------------------------------------------------------
+template <typename ST>
+__global__ void moe_router_kernel(float* __restrict__ route, int* __restrict__ top_idx, float* __restrict__ top_w, const ST* __restrict__ h,
+                                  const float* __restrict__ w_router, int W, int E, int top) {
+  extern __shared__ float dyn[];  // h [W] | scores [E]
+  float* hs = dyn;
+  float* z = dyn + W;
+  const int t = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nw = blockDim.x >> 5;
+  for (int i = tid; i < W; i += blockDim.x) hs[i] = ldf(h + (size_t)t * W + i);
+  __syncthreads();
+  for (int e = warp; e < E; e += nw) {
+    const float* wr = w_router + (size_t)e * W;
+    float d = 0.f;
+    for (int i = lane; i < W; i += 32) d += hs[i] * wr[i];
+    d = warp_sum(d);
+    if (lane == 0) z[e] = d;
+  }
+  __syncthreads();
+  if (warp != 0) return;
+  float mx = -INFINITY;
+  for (int e = lane; e < E; e += 32) mx = fmaxf(mx, z[e]);
+  mx = warp_max(mx);
+  float sum = 0.f;
+  for (int e = lane; e < E; e += 32) sum += expf(z[e] - mx);
+  sum = warp_sum(sum);
+  const float inv = 1.f / sum;
+  for (int e = lane; e < E; e += 32) {
+    z[e] = expf(z[e] - mx) * inv;
+    route[(size_t)t * E + e] = 0.f;
+  }
+  __syncwarp();
+  for (int k = 0; k < top; ++k) {
+    float best = -1.f;
+    int bi = E;
+    for (int e = lane; e < E; e += 32)
+      if (z[e] > best) { best = z[e]; bi = e; }  // strict: the lowest index of a lane's equal scores stays
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
+    }
+    if (lane == 0) {
+      route[(size_t)t * E + bi] = best;
+      top_idx[(size_t)t * top + k] = bi;
+      top_w[(size_t)t * top + k] = best;
+      z[bi] = -1.f;  // scores are positive: taken
+    }
+    __syncwarp();
+  }
+}
+
+// Activation of all experts of a token at once.  in row: [F gate | F up] with F = E * ff + ff_shared columns, expert e's at [e ff, (e + 1) ff),
+// the shared expert's last.  g = min(gate, limit), u = clamp(up, -limit, limit), act = g sigmoid(alpha g) (u + 1);
+// out[t][j] = route[t][expert of j] * act (shared columns: weight 1).  An expert that the token does not use contributes exact zeros.
+template <typename ST>
+__global__ void moe_act_kernel(ST* __restrict__ out, const ST* __restrict__ in, const float* __restrict__ route, int E, int ff, float limit,
+                               int ff_shared, float limit_shared, float alpha) {
+  const int t = blockIdx.x;
+  const int F = E * ff + ff_shared;
+  const int j = blockIdx.y * blockDim.x + threadIdx.x;
+  if (j >= F) return;
+  float wgt = 1.f, lim = limit_shared;
+  if (j < E * ff) {
+    wgt = route[(size_t)t * E + j / ff];
+    lim = limit;
+  }
+  float y = 0.f;
+  if (wgt != 0.f) {
+    const float g = fminf(ldf(in + (size_t)t * 2 * F + j), lim);
+    const float u = fminf(fmaxf(ldf(in + (size_t)t * 2 * F + F + j), -lim), lim);
+    y = wgt * (g / (1.f + expf(-alpha * g))) * (u + 1.f);
+  }
+  stf(out + (size_t)t * F + j, y);
+}
+
+}  // namespace
+}  // namespace qs
+
+using namespace qs;
+
+#define QS_DT(dtype, CALL_BF16, CALL_F32)                                               \
+  do {                                                                                  \
+    if ((dtype) == QS_DTYPE_BF16) { CALL_BF16; }                                        \
+    else if ((dtype) == QS_DTYPE_F32) { CALL_F32; }                                     \
+    else return set_error(qs::QS_ERR_INVALID, "dtype must be QS_DTYPE_BF16 or QS_DTYPE_F32"); \
+  } while (0)
+
+extern "C" {
+
+int qs_hyb_stream_norm(void* out_h, float* out_sum, float* x, int streams, const void* upd, int upd_f32, const float* upd_mix, const float* upd_out,
+                       const float* in_coef, const float* w, int groups, float offset, float eps, int tokens_n, int width, int dtype, void* stream) {
+  QS_REQUIRE(x && (out_h == nullptr || w != nullptr), "hyb_stream_norm: null tensor");
+  QS_REQUIRE(streams >= 1 && streams <= kMaxStreams, "hyb_stream_norm: 1..8 streams");
+  QS_REQUIRE(upd == nullptr || (upd_mix && upd_out), "hyb_stream_norm: a pending write needs its coefficients");
+  QS_REQUIRE(groups >= 1 && width % groups == 0, "hyb_stream_norm: the width must split into `groups` equal parts");
+  if (tokens_n == 0) return qs::QS_OK;
+  cudaStream_t s = (cudaStream_t)stream;
+  const int threads = width >= 2048 ? 256 : 128;
+  const int per = std::max(1, threads / 32 / groups);
+  const size_t smb = ((size_t)width + (size_t)groups * per + groups) * sizeof(float);
+  QS_REQUIRE(smb <= 200 * 1024, "hyb_stream_norm: row too wide for shared memory");
+#define QS_LAUNCH(ST)                                                                                                                   \
+  do {                                                                                                                                  \
+    if (smb > 48 * 1024) cudaFuncSetAttribute(stream_norm_kernel<ST>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smb);           \
+    stream_norm_kernel<ST><<<tokens_n, threads, smb, s>>>((ST*)out_h, out_sum, x, streams, upd, upd_f32, upd_mix, upd_out, in_coef, w,  \
+                                                         groups, offset, eps, width);                                                  \
+  } while (0)
+  QS_DT(dtype, QS_LAUNCH(__nv_bfloat16), QS_LAUNCH(float));
+#undef QS_LAUNCH
+  return check_cuda(cudaGetLastError(), "hyb_stream_norm");
+}
+
+int qs_hyb_branch_norm_mean(float* y, const void* a, const void* b, const float* wa, const float* wb, float scale, float eps, int tokens_n,
+                            int width, int dtype, void* stream) {
+  QS_REQUIRE(y && a && b && wa && wb, "hyb_branch_norm_mean: null tensor");
+  if (tokens_n == 0) return qs::QS_OK;
+  cudaStream_t s = (cudaStream_t)stream;
+  const int threads = width >= 1024 ? 256 : 128;
+  QS_DT(dtype,
+        (branch_norm_mean_kernel<__nv_bfloat16><<<tokens_n, threads, 0, s>>>(y, (const __nv_bfloat16*)a, (const __nv_bfloat16*)b, wa, wb, scale, eps, width)),
+        (branch_norm_mean_kernel<float><<<tokens_n, threads, 0, s>>>(y, (const float*)a, (const float*)b, wa, wb, scale, eps, width)));
+  return check_cuda(cudaGetLastError(), "hyb_branch_norm_mean");
+}
+
+int qs_hyb_qk_prepare_append(void* proj, int64_t stride, const float* bias, const float* q_factor, const int32_t* tok_slot, const int32_t* tok_pos,
+                             const int32_t* block_table, int max_blocks, void* kpool, void* vpool, const float* inv_freq, int rot_layout,
+                             int rot_dims, int unit_rms, float eps, int tokens_n, int heads, int kv_heads, int dim, int vdim, int page_size,
+                             int dtype, void* stream) {
+  QS_REQUIRE(proj && tok_slot && tok_pos && block_table && kpool && vpool, "hyb_qk_prepare_append: null tensor");
+  QS_REQUIRE(rot_dims >= 0 && rot_dims % 2 == 0 && rot_dims <= dim && (rot_dims == 0 || inv_freq != nullptr) && (rot_layout == 0 || rot_layout == 1),
+             "hyb_qk_prepare_append: bad rotary size or layout");
+  QS_REQUIRE(kv_heads > 0 && heads % kv_heads == 0 && page_size > 0 && dim > 0 && dim <= 8192, "hyb_qk_prepare_append: bad head geometry");
+  if (tokens_n == 0) return qs::QS_OK;
+  cudaStream_t s = (cudaStream_t)stream;
+  dim3 grid(tokens_n, heads + kv_heads);
+  const size_t smb = (size_t)dim * sizeof(float);
+  QS_DT(dtype,
+        (qk_prepare_append_kernel<__nv_bfloat16><<<grid, 64, smb, s>>>((__nv_bfloat16*)proj, stride, bias, q_factor, tok_slot, tok_pos, block_table,
+                                                                        max_blocks, (__nv_bfloat16*)kpool, (__nv_bfloat16*)vpool, inv_freq, rot_layout,
+                                                                        rot_dims, unit_rms, eps, heads, kv_heads, dim, vdim, page_size)),
+        (qk_prepare_append_kernel<float><<<grid, 64, smb, s>>>((float*)proj, stride, bias, q_factor, tok_slot, tok_pos, block_table, max_blocks,
+                                                                (float*)kpool, (float*)vpool, inv_freq, rot_layout, rot_dims, unit_rms, eps, heads,
+                                                                kv_heads, dim, vdim, page_size)));
+  return check_cuda(cudaGetLastError(), "hyb_qk_prepare_append");
+}
+
+int qs_hyb_moe_router(float* route, int32_t* top_idx, float* top_w, const void* h, const float* w_router, int tokens_n, int width, int experts,
+                      int top, int dtype, void* stream) {
+  QS_REQUIRE(route && top_idx && top_w && h && w_router, "hyb_moe_router: null tensor");
+  QS_REQUIRE(experts >= 1 && top >= 1 && top <= experts, "hyb_moe_router: 1 <= top <= experts");
+  if (tokens_n == 0) return qs::QS_OK;
+  cudaStream_t s = (cudaStream_t)stream;
+  const size_t smb = ((size_t)width + experts) * sizeof(float);
+  QS_REQUIRE(smb <= 200 * 1024, "hyb_moe_router: row too wide for shared memory");
+#define QS_LAUNCH(ST)                                                                                                              \
+  do {                                                                                                                             \
+    if (smb > 48 * 1024) cudaFuncSetAttribute(moe_router_kernel<ST>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smb);       \
+    moe_router_kernel<ST><<<tokens_n, 256, smb, s>>>(route, top_idx, top_w, (const ST*)h, w_router, width, experts, top);          \
+  } while (0)
+  QS_DT(dtype, QS_LAUNCH(__nv_bfloat16), QS_LAUNCH(float));
+#undef QS_LAUNCH
+  return check_cuda(cudaGetLastError(), "hyb_moe_router");
+}
+
+int qs_hyb_moe_act(void* out, const void* in, const float* route, int tokens_n, int experts, int ff, float limit, int ff_shared, float limit_shared,
+                   float alpha, int dtype, void* stream) {
+  QS_REQUIRE(out && in && (route || experts == 0), "hyb_moe_act: null tensor");
+  QS_REQUIRE(experts >= 0 && ff >= 0 && ff_shared >= 0 && experts * ff + ff_shared > 0, "hyb_moe_act: no columns");
+  if (tokens_n == 0) return qs::QS_OK;
+  cudaStream_t s = (cudaStream_t)stream;
+  const int F = experts * ff + ff_shared;
+  dim3 grid(tokens_n, (F + 255) / 256);
+  QS_DT(dtype,
+        (moe_act_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((__nv_bfloat16*)out, (const __nv_bfloat16*)in, route, experts, ff, limit, ff_shared,
+                                                             limit_shared, alpha)),
+        (moe_act_kernel<float><<<grid, 256, 0, s>>>((float*)out, (const float*)in, route, experts, ff, limit, ff_shared, limit_shared, alpha)));
+  return check_cuda(cudaGetLastError(), "hyb_moe_act");
+}
+
+}  // extern "C"

@@ -19,7 +19,8 @@ import torch
 
 from ._lib import check, lib
 from .cache import HybridCache
-from .modelcfg import AttentionMixerConfig, DeltaMixerConfig, HybridConfig
+from .modelcfg import (AttentionMixerConfig, DeltaMixerConfig, GateRecurrenceMixerConfig, HybridConfig, MlpConfig, MoeConfig, ParallelMixerConfig,
+                       RetentionMixerConfig)
 
 _DT = {torch.bfloat16: 0, torch.float32: 1}
 
@@ -109,13 +110,38 @@ class StepBatch:
 # ------------------------------------------------------------------------------------------------------------------------
 # mixers
 # ------------------------------------------------------------------------------------------------------------------------
-class MultiMapAttentionMixer:
+class _Mixer:
+    """What the decoder needs of a sequence mixer: `w_in` [in_features, W] (one product makes the mixer's projection rows), `run` (projection
+    rows -> head outputs [T, out_features], through the mixer's cache or state), `w_out` [W, out_features]."""
+
+    def place_out(self, st) -> None:
+        """Keep the output projection on the device (blocks that do not fold it into a product of their own)."""
+        self.w_out = st(self.w_out)
+
+    def project(self, cat: torch.Tensor, dt: int, stream):
+        """Head outputs -> the mixer's output rows [T, W]; returns (rows, rows are fp32)."""
+        return torch.mm(cat, self.w_out.t()), False
+
+
+class MultiMapAttentionMixer(_Mixer):
     """Causal softmax attention over the paged cache with `maps` score maps per head sharing the values; maps = 2 is differential attention:
-    o = a1 - lambda a2 with lambda = exp(lq1 . lk1) - exp(lq2 . lk2) + diff, then unit RMS per head and a factor (1 - diff)."""
+    o = a1 - lambda a2 with lambda = exp(lq1 . lk1) - exp(lq2 . lk2) + diff, then unit RMS per head and a factor (1 - diff).
+    With one map: optional projection biases, unit-RMS q / k, a learned temperature per head (folded into the prepared query), a sink term in
+    the denominator, and a mask by chunks of positions and / or a window."""
 
     def __init__(self, m: AttentionMixerConfig, w: Dict[str, torch.Tensor], eps: float, dtype, device):
         self.m, self.eps = m, eps
         assert m.heads % m.kv_heads == 0
+        f32 = lambda t: t.to(torch.float32).to(device).contiguous()
+        self.general = m.rot is None or m.rot.layout != "interleaved" or m.bias or m.qk_norm or m.head_temp
+        if (self.general or m.sink) and m.maps != 1:
+            raise ValueError("biases, unit-RMS q / k, head temperatures, sinks and non-interleaved rotations need one score map per head")
+        self.bias = f32(torch.cat([w["q.b"], w["k.b"], w["v.b"]], 0)) if m.bias else None
+        self.temp = f32(w["temp"]) if m.head_temp else None
+        self.sinks = f32(w["sink"]) if m.sink else None
+        for t, n in ((self.temp, "temp"), (self.sinks, "sink")):
+            if t is not None and t.numel() != m.heads:
+                raise ValueError(f"attention weight {n} must have one number per head")
         self.in_features = (m.heads + m.kv_heads) * m.maps * m.dim + m.kv_heads * m.vdim
         self.out_features = m.heads * m.vdim
         for name, rows in (("q", m.heads * m.maps * m.dim), ("k", m.kv_heads * m.maps * m.dim), ("v", m.kv_heads * m.vdim)):
@@ -123,8 +149,12 @@ class MultiMapAttentionMixer:
                 raise ValueError(f"attention weight {name}: {tuple(w[name].shape)} does not have {rows} rows")
         self.w_in = torch.cat([w["q"], w["k"], w["v"]], 0).to(device=device, dtype=dtype).contiguous()
         self.w_out = w["o"]
-        self.inv_freq = torch.tensor(m.rot.inv_freq(), dtype=torch.float64).to(torch.float32).to(device)
-        self.amp = float(m.rot.amplitude())
+        self.inv_freq = torch.tensor(m.rot.inv_freq(), dtype=torch.float64).to(torch.float32).to(device) if m.rot is not None else None
+        self.amp = float(m.rot.amplitude()) if m.rot is not None else 1.0
+        if self.general and self.amp != 1.0:
+            raise ValueError("scaled rotary frequencies are only built for the interleaved layout")
+        if self.bias is not None and self.bias.numel() != self.in_features:
+            raise ValueError("attention biases do not match the projections")
         if m.maps == 2:
             d = lambda a, b: float((w[a].double() * w[b].double()).sum())
             self.lam = math.exp(d("lq1", "lk1")) - math.exp(d("lq2", "lk2")) + m.diff
@@ -138,10 +168,19 @@ class MultiMapAttentionMixer:
 
     def run(self, proj: torch.Tensor, out: torch.Tensor, b: StepBatch, run_cache: dict, page_size: int, scratch, dt: int, stream) -> None:
         m = self.m
-        fast = scratch is not None and lib.qs_hyb_attention_fast_supported(dt, m.heads, m.kv_heads, m.maps, m.dim, m.vdim, proj.stride(0)) == 1
-        check(lib.qs_hyb_rope_append(proj.data_ptr(), proj.stride(0), _p(b.tok_slot), _p(b.tok_pos), _p(b.block_table), b.block_table.shape[1],
-                                     run_cache["k"].data_ptr(), run_cache["v"].data_ptr(), self.inv_freq.data_ptr(), self.amp, b.n_tokens,
-                                     m.heads, m.kv_heads, m.maps, m.dim, m.vdim, m.rot.dims, page_size, dt, stream))
+        masked = m.chunk > 0 or m.window > 0 or m.sink
+        fast = not masked and scratch is not None and \
+            lib.qs_hyb_attention_fast_supported(dt, m.heads, m.kv_heads, m.maps, m.dim, m.vdim, proj.stride(0)) == 1
+        if self.general:
+            check(lib.qs_hyb_qk_prepare_append(proj.data_ptr(), proj.stride(0), _p(self.bias), _p(self.temp), _p(b.tok_slot), _p(b.tok_pos),
+                                               _p(b.block_table), b.block_table.shape[1], run_cache["k"].data_ptr(), run_cache["v"].data_ptr(),
+                                               _p(self.inv_freq), 1 if m.rot is not None and m.rot.layout == "half" else 0,
+                                               m.rot.dims if m.rot is not None else 0, 1 if m.qk_norm else 0, self.eps, b.n_tokens, m.heads,
+                                               m.kv_heads, m.dim, m.vdim, page_size, dt, stream))
+        else:
+            check(lib.qs_hyb_rope_append(proj.data_ptr(), proj.stride(0), _p(b.tok_slot), _p(b.tok_pos), _p(b.block_table), b.block_table.shape[1],
+                                         run_cache["k"].data_ptr(), run_cache["v"].data_ptr(), self.inv_freq.data_ptr(), self.amp, b.n_tokens,
+                                         m.heads, m.kv_heads, m.maps, m.dim, m.vdim, m.rot.dims, page_size, dt, stream))
         if fast:
             # prompt portions as 64-row tiles on the tensor cores, single tokens and short portions with a head group as the tile's rows
             check(lib.qs_hyb_attention_fast(out.data_ptr(), out.stride(0), proj.data_ptr(), proj.stride(0), run_cache["k"].data_ptr(),
@@ -154,10 +193,10 @@ class MultiMapAttentionMixer:
         check(lib.qs_hyb_attention(out.data_ptr(), out.stride(0), proj.data_ptr(), proj.stride(0), run_cache["k"].data_ptr(),
                                    run_cache["v"].data_ptr(), _p(b.tok_slot), _p(b.tok_pos), _p(b.block_table), b.block_table.shape[1],
                                    b.n_tokens, m.heads, m.kv_heads, m.maps, m.dim, m.vdim, m.scale, self.lam, self.out_scale, self.eps,
-                                   1 if m.head_norm else 0, page_size, dt, stream))
+                                   1 if m.head_norm else 0, page_size, m.chunk, m.window, _p(self.sinks), dt, stream))
 
 
-class GatedDeltaMixer:
+class GatedDeltaMixer(_Mixer):
     """Gated delta rule with short convolutions; the state and the convolution's last inputs live in the sequence's slot."""
 
     def __init__(self, m: DeltaMixerConfig, w: Dict[str, torch.Tensor], eps: float, dtype, device):
@@ -192,20 +231,198 @@ class GatedDeltaMixer:
                                      m.conv, m.unit_eps, self.eps, dt, stream))
 
 
-MIXERS = {AttentionMixerConfig: MultiMapAttentionMixer, DeltaMixerConfig: GatedDeltaMixer}
+class GateRecurrenceMixer(_Mixer):
+    """HGRN2: q = silu(W_q h), forget gate f = lower + (1 - lower) sigmoid(W_f h + b) per head and row, S <- diag(f) S + (1 - f) v^T, o = S^T q,
+    unit RMS per head with a gain shared by the heads.  The fp32 state lives in the sequence's slot."""
+
+    def __init__(self, m: GateRecurrenceMixerConfig, w: Dict[str, torch.Tensor], eps: float, dtype, device):
+        self.m, self.eps = m, eps
+        hd, hv = m.heads * m.dim, m.heads * m.vdim
+        for name, rows in (("q", hd), ("f", hd), ("v", hv)):
+            if w[name].shape[0] != rows:
+                raise ValueError(f"gate recurrence weight {name}: {tuple(w[name].shape)} does not have {rows} rows")
+        self.in_features, self.out_features = 2 * hd + hv, hv
+        self.w_in = torch.cat([w["q"], w["f"], w["v"]], 0).to(device=device, dtype=dtype).contiguous()
+        self.w_out = w["o"]
+        f32 = lambda t: t.to(torch.float32).to(device).contiguous()
+        self.f_bias, self.lower, self.norm_w = f32(w["f.b"]), f32(w["lower"]), f32(w["norm"])
+        if self.f_bias.numel() != hd or self.lower.numel() != hd or self.norm_w.numel() != m.vdim:
+            raise ValueError("gate recurrence: f.b and lower have heads * dim entries, norm has vdim")
+
+    def scratch_floats(self, tokens: int) -> int:
+        return tokens * (self.in_features + self.out_features)
+
+    def run(self, proj, out, b: StepBatch, run_cache: dict, page_size: int, scratch: torch.Tensor, dt: int, stream) -> None:
+        m, T = self.m, b.n_tokens
+        prep = scratch[: T * self.in_features]
+        o_raw = scratch[T * self.in_features: T * (self.in_features + self.out_features)]
+        check(lib.qs_hyb_gate_recurrence(out.data_ptr(), out.stride(0), prep.data_ptr(), o_raw.data_ptr(), proj.data_ptr(), proj.stride(0),
+                                         self.f_bias.data_ptr(), self.lower.data_ptr(), self.norm_w.data_ptr(), run_cache["state"].data_ptr(),
+                                         _p(b.entry_start), _p(b.entry_len), _p(b.entry_slot), _p(b.entry_pos0), T, b.n_entries, m.heads, m.dim,
+                                         m.vdim, self.eps, dt, stream))
+
+
+class RetentionMixer(_Mixer):
+    """Retention: S <- decay_h S + k v^T, o = S^T q with rotary q / k (k times dim^-1/2 after the rotation), unit-RMS heads times silu of an
+    output gate.  The fp32 state lives in the sequence's slot."""
+
+    def __init__(self, m: RetentionMixerConfig, w: Dict[str, torch.Tensor], eps: float, dtype, device):
+        self.m, self.eps = m, eps
+        hd, hv = m.heads * m.dim, m.heads * m.vdim
+        names = (("q", hd), ("k", hd), ("v", hv)) + ((("g", hv),) if m.gated else ())
+        for name, rows in names:
+            if w[name].shape[0] != rows:
+                raise ValueError(f"retention weight {name}: {tuple(w[name].shape)} does not have {rows} rows")
+        self.in_features, self.out_features = sum(r for _, r in names), hv
+        self.prep_width = 2 * hd + hv
+        self.w_in = torch.cat([w[n] for n, _ in names], 0).to(device=device, dtype=dtype).contiguous()
+        self.w_out = w["o"]
+        if m.rot is not None and (m.rot.layout != "half" or m.rot.factor is not None):
+            raise ValueError("retention rotates pairs (i, i + dims/2) with unscaled frequencies")
+        self.inv_freq = torch.tensor(m.rot.inv_freq(), dtype=torch.float64).to(torch.float32).to(device) if m.rot is not None else None
+        self.decay = torch.tensor(m.decay, dtype=torch.float64).to(torch.float32).to(device)
+
+    def scratch_floats(self, tokens: int) -> int:
+        return tokens * (self.prep_width + self.out_features)
+
+    def run(self, proj, out, b: StepBatch, run_cache: dict, page_size: int, scratch: torch.Tensor, dt: int, stream) -> None:
+        m, T = self.m, b.n_tokens
+        prep = scratch[: T * self.prep_width]
+        o_raw = scratch[T * self.prep_width: T * (self.prep_width + self.out_features)]
+        check(lib.qs_hyb_retention(out.data_ptr(), out.stride(0), prep.data_ptr(), o_raw.data_ptr(), proj.data_ptr(), proj.stride(0),
+                                   self.decay.data_ptr(), _p(self.inv_freq), m.rot.dims if m.rot is not None else 0, float(m.dim) ** -0.5,
+                                   1 if m.gated else 0, run_cache["state"].data_ptr(), _p(b.tok_pos), _p(b.entry_start), _p(b.entry_len),
+                                   _p(b.entry_slot), _p(b.entry_pos0), T, b.n_entries, m.heads, m.dim, m.vdim, self.eps, dt, stream))
+
+
+class ParallelMixer(_Mixer):
+    """Two mixers on the same input: one product makes both projection rows, each runs on its part, and the result is
+    scale (norm(W_o,left heads_left) gain_left + norm(W_o,right heads_right) gain_right) with plain RMS norms over the width."""
+
+    def __init__(self, m: ParallelMixerConfig, w: Dict[str, torch.Tensor], eps: float, dtype, device):
+        self.m, self.eps = m, eps
+        sub = lambda side: {k[len(side) + 1:]: t for k, t in w.items() if k.startswith(side + ".") and k != side + ".out"}
+        self.left = MIXERS[type(m.left)](m.left, sub("left"), eps, dtype, device)
+        self.right = MIXERS[type(m.right)](m.right, sub("right"), eps, dtype, device)
+        self.in_features = self.left.in_features + self.right.in_features
+        self.out_features = self.left.out_features + self.right.out_features
+        self.w_in = torch.cat([self.left.w_in, self.right.w_in], 0).contiguous()
+        del self.left.w_in, self.right.w_in
+        f32 = lambda t: t.to(torch.float32).to(device).contiguous()
+        self.gain_left, self.gain_right = f32(w["left.out"]), f32(w["right.out"])
+
+    def scratch_floats(self, tokens: int) -> int:
+        return max(self.left.scratch_floats(tokens), self.right.scratch_floats(tokens))  # they run one after the other
+
+    def place_out(self, st) -> None:
+        self.left.place_out(st)
+        self.right.place_out(st)
+
+    def run(self, proj, out, b: StepBatch, run_cache: dict, page_size: int, scratch, dt: int, stream) -> None:
+        a, oa = self.left.in_features, self.left.out_features
+        self.left.run(proj[:, :a], out[:, :oa], b, run_cache["left"], page_size, scratch, dt, stream)
+        self.right.run(proj[:, a:], out[:, oa:], b, run_cache["right"], page_size, scratch, dt, stream)
+
+    def project(self, cat: torch.Tensor, dt: int, stream):
+        oa = self.left.out_features
+        yl, fl = self.left.project(cat[:, :oa], dt, stream)
+        yr, fr = self.right.project(cat[:, oa:], dt, stream)
+        if fl or fr:
+            raise NotImplementedError("side-by-side mixers whose own outputs are fp32 rows")
+        T, W = yl.shape
+        y = torch.empty((T, W), dtype=torch.float32, device=cat.device)
+        check(lib.qs_hyb_branch_norm_mean(y.data_ptr(), yl.data_ptr(), yr.data_ptr(), self.gain_left.data_ptr(), self.gain_right.data_ptr(),
+                                          self.m.scale, self.eps, T, W, dt, stream))
+        return y, True
+
+
+MIXERS = {AttentionMixerConfig: MultiMapAttentionMixer, DeltaMixerConfig: GatedDeltaMixer, GateRecurrenceMixerConfig: GateRecurrenceMixer,
+          RetentionMixerConfig: RetentionMixer, ParallelMixerConfig: ParallelMixer}
+
+
+# ------------------------------------------------------------------------------------------------------------------------
+# feed-forwards of sequential blocks
+# ------------------------------------------------------------------------------------------------------------------------
+class MoeFeedForward:
+    """Mixture of experts with an optional shared expert as ONE pair of products: the gate / up rows of all experts (and the shared one) are
+    stacked, the activation kernel weights an expert's columns with the token's router score for it (exact zeros for experts the token does
+    not use), and the stacked down projection sums the weighted experts in its fp32 accumulation.  The router (fp32 logits, softmax, top
+    scores) is one kernel."""
+
+    def __init__(self, c: MoeConfig, w: Dict[str, torch.Tensor], width: int, dtype, device):
+        self.c = c
+        st = lambda t: t.to(device=device, dtype=dtype).contiguous()
+        names = [f"e{e}" for e in range(c.experts)] + (["shared"] if c.shared_ff else [])
+        for n in names:
+            ff = c.shared_ff if n == "shared" else c.ff
+            for part, shape in (("gate", (ff, width)), ("up", (ff, width)), ("down", (width, ff))):
+                if tuple(w[f"{n}.{part}"].shape) != shape:
+                    raise ValueError(f"expert weight {n}.{part}: {tuple(w[f'{n}.{part}'].shape)} is not {shape}")
+        self.F = c.experts * c.ff + c.shared_ff
+        self.w_in = st(torch.cat([w[f"{n}.gate"] for n in names] + [w[f"{n}.up"] for n in names], 0))  # [2 F, W]
+        self.w_down = st(torch.cat([w[f"{n}.down"] for n in names], 1))                               # [W, F]
+        self.w_router = w["router"].to(torch.float32).to(device).contiguous()
+        if tuple(self.w_router.shape) != (c.experts, width):
+            raise ValueError("router weight is not [experts, width]")
+
+    def run(self, h: torch.Tensor, dt: int, stream) -> torch.Tensor:
+        c, T, W = self.c, h.shape[0], h.shape[1]
+        dev = h.device
+        route = torch.empty((T, c.experts), dtype=torch.float32, device=dev)
+        top_idx = torch.empty((T, c.top), dtype=torch.int32, device=dev)
+        top_w = torch.empty((T, c.top), dtype=torch.float32, device=dev)
+        check(lib.qs_hyb_moe_router(route.data_ptr(), top_idx.data_ptr(), top_w.data_ptr(), h.data_ptr(), self.w_router.data_ptr(), T, W, c.experts,
+                                    c.top, dt, stream))
+        gu = torch.mm(h, self.w_in.t())
+        act = torch.empty((T, self.F), dtype=h.dtype, device=dev)
+        check(lib.qs_hyb_moe_act(act.data_ptr(), gu.data_ptr(), route.data_ptr(), T, c.experts, c.ff, c.limit, c.shared_ff, c.shared_limit, c.alpha,
+                                 dt, stream))
+        return torch.mm(act, self.w_down.t())
+
+
+class DenseFeedForward:
+    """W_down (gelu_tanh(W_gate h) * W_up h)."""
+
+    def __init__(self, c: MlpConfig, w: Dict[str, torch.Tensor], width: int, dtype, device):
+        st = lambda t: t.to(device=device, dtype=dtype).contiguous()
+        self.ff = c.ff
+        self.w_in, self.w_down = st(torch.cat([w["gate"], w["up"]], 0)), st(w["down"])
+
+    def run(self, h: torch.Tensor, dt: int, stream) -> torch.Tensor:
+        gu = torch.mm(h, self.w_in.t())
+        act = torch.empty((h.shape[0], self.ff), dtype=h.dtype, device=h.device)
+        check(lib.qs_hyb_gelu_tanh_mul(act.data_ptr(), act.stride(0), gu.data_ptr(), h.shape[0], self.ff, dt, stream))
+        return torch.mm(act, self.w_down.t())
+
+
+FEED_FORWARDS = {MoeConfig: MoeFeedForward, MlpConfig: DenseFeedForward}
+
+
+@dataclass
+class _Hyper:
+    """Coefficients of one sublayer's connection to the residual streams: read (`cin` [s]), write (`cout` [s]) and mix [from, to]."""
+    cin: torch.Tensor
+    cout: torch.Tensor
+    mix: torch.Tensor
 
 
 # ------------------------------------------------------------------------------------------------------------------------
 # the decoder
 # ------------------------------------------------------------------------------------------------------------------------
 class _Layer:
-    def __init__(self, mixer, norm1, norm2, w_mlp_in, w_out, ff):
+    def __init__(self, mixer, norm1, norm2, w_mlp_in, w_out, ff, hc1=None, hc2=None):
         self.mixer, self.norm1, self.norm2, self.w_mlp_in, self.w_out, self.ff = mixer, norm1, norm2, w_mlp_in, w_out, ff
+        self.hc1, self.hc2 = hc1, hc2
 
 
 class HybridDecoder:
-    """x <- x + (mixer(norm1 x) + ff(norm2 x)) per layer run, both branches of the same x; the two output projections are ONE product:
-    [mixer heads | ff activation] @ [W_o | W_down]^T, so the sum of the branches is accumulated in fp32 inside the GEMM."""
+    """Two block forms (HybridConfig.block):
+
+    "parallel":   x <- x + (mixer(norm1 x) + ff(norm2 x)) per layer run, both branches of the same x; the two output projections are ONE
+                  product: [mixer heads | ff activation] @ [W_o | W_down]^T, so the sum of the branches is accumulated in fp32 inside the GEMM.
+    "sequential": x <- x + mixer(norm1 x), then x <- x + ff(norm2 x), on `streams` residual streams [T, streams, W] whose read, write and
+                  mixing coefficients belong to the sublayer (one stream with coefficients 1 is the plain residual).  A sublayer's write to
+                  the streams happens inside the next sublayer's norm kernel."""
 
     def __init__(self, cfg: HybridConfig, weights: Dict[str, torch.Tensor], dtype: torch.dtype = torch.bfloat16, device: Optional[torch.device] = None):
         if dtype not in _DT:
@@ -229,10 +446,32 @@ class HybridDecoder:
         self.head = st(weights["head"])
         self.final_norm = f32(weights["final.norm"])
         self.layers: List[_Layer] = []
+        if cfg.block not in ("parallel", "sequential"):
+            raise ValueError(f"unknown block form {cfg.block!r}")
+        self.n_streams = max(cfg.streams, 1) if cfg.block == "sequential" else 1
+        one = torch.ones(1, dtype=torch.float32, device=dev)
+
+        def hyper(pre: str) -> _Hyper:
+            if cfg.streams <= 0:
+                return _Hyper(one, one, one)
+            h = _Hyper(f32(weights[pre + "in"]), f32(weights[pre + "out"]), f32(weights[pre + "mix"]))
+            if h.cin.numel() != cfg.streams or h.cout.numel() != cfg.streams or tuple(h.mix.shape) != (cfg.streams, cfg.streams):
+                raise ValueError(f"{pre}*: hyper-connection coefficients do not match {cfg.streams} streams")
+            return h
+
         for i, ly in enumerate(cfg.layers):
             pre = f"l{i}."
             mw = {k[len(pre) + 4:]: v for k, v in weights.items() if k.startswith(pre + "mix.")}
             mixer = MIXERS[type(ly.mixer)](ly.mixer, mw, cfg.eps, dtype, dev)
+            if cfg.block == "sequential":
+                mixer.place_out(st)
+                ff, norm2, hc2 = None, None, None
+                if ly.mlp is not None:
+                    fw = {k[len(pre) + 4:]: v for k, v in weights.items() if k.startswith(pre + "mlp.")}
+                    ff = FEED_FORWARDS[type(ly.mlp)](ly.mlp, fw, W, dtype, dev)
+                    norm2, hc2 = f32(weights[pre + "norm2"]), hyper(pre + "hc2.")
+                self.layers.append(_Layer(mixer, f32(weights[pre + "norm1"]), norm2, None, None, ff, hyper(pre + "hc1."), hc2))
+                continue
             outs = [mixer.w_out]
             w_mlp_in, norm2, ff = None, None, 0
             if ly.mlp is not None:
@@ -267,14 +506,16 @@ class HybridDecoder:
         `scratch` (fp32, at least scratch_floats(T)): the caller's own work space, e.g. one that a captured CUDA graph keeps."""
         cfg, dev, dt, T, W = self.cfg, self.device, self.dt, b.n_tokens, self.cfg.width
         s = _stream(dev)
-        x = torch.empty((T, W), dtype=torch.float32, device=dev)
+        x = torch.empty((T, self.n_streams, W) if cfg.block == "sequential" else (T, W), dtype=torch.float32, device=dev)
         check(lib.qs_hyb_embed(x.data_ptr(), _p(b.tokens), _p(b.prev), self.embed.data_ptr(), _p(self.pair), T, W, cfg.pair_buckets,
-                               cfg.pair_mul_prev, cfg.pair_mul_cur, dt, s))
+                               cfg.pair_mul_prev, cfg.pair_mul_cur, cfg.embed_scale, self.n_streams, dt, s))
         if scratch is None:
             need = self.scratch_floats(T)
             if need and (self._scratch is None or self._scratch.numel() < need):
                 self._scratch = torch.empty(need, dtype=torch.float32, device=dev)
             scratch = self._scratch
+        if cfg.block == "sequential":
+            return self._forward_sequential(x, b, cache, tap, scratch, s)
         h1 = torch.empty((T, W), dtype=self.dtype, device=dev)
         h2 = torch.empty((T, W), dtype=self.dtype, device=dev)
         upd = None  # the previous layer's update, still to be added to the stream
@@ -297,11 +538,48 @@ class HybridDecoder:
             check(lib.qs_hyb_residual_add(x.data_ptr(), upd.data_ptr(), T * W, dt, s))
         return x
 
+    def _stream_norm(self, out_h, out_sum, x, pending, cin, w, s) -> None:
+        """Land the pending sublayer write (rows, rows are fp32, its connection) in the streams, then read them: the norm of sum_s cin[s] x_s
+        into out_h and / or that sum itself (cin None: the plain sum) into out_sum."""
+        cfg = self.cfg
+        y, y32, hc = pending if pending is not None else (None, False, None)
+        check(lib.qs_hyb_stream_norm(_p(out_h), _p(out_sum), x.data_ptr(), self.n_streams, _p(y), 1 if y32 else 0, _p(hc.mix) if hc else None,
+                                     _p(hc.cout) if hc else None, _p(cin), _p(w), cfg.norm_groups, cfg.norm_offset, cfg.eps, x.shape[0], cfg.width,
+                                     self.dt, s))
+
+    def _forward_sequential(self, x, b: StepBatch, cache: HybridCache, tap, scratch, s) -> torch.Tensor:
+        dev, dt, T, W = self.device, self.dt, b.n_tokens, self.cfg.width
+        pending = None  # the last sublayer's write to the streams, still to land
+        h = torch.empty((T, W), dtype=self.dtype, device=dev)
+        for run, li in enumerate(self.schedule):
+            ly = self.layers[li]
+            self._stream_norm(h, None, x, pending, ly.hc1.cin, ly.norm1, s)
+            proj = torch.mm(h, ly.mixer.w_in.t())
+            cat = torch.empty((T, ly.mixer.out_features), dtype=self.dtype, device=dev)
+            ly.mixer.run(proj, cat, b, cache.runs[run], cache.page_size, scratch, dt, s)
+            y, y32 = ly.mixer.project(cat, dt, s)
+            pending = (y, y32, ly.hc1)
+            if ly.ff is not None:
+                self._stream_norm(h, None, x, pending, ly.hc2.cin, ly.norm2, s)
+                pending = (ly.ff.run(h, dt, s), False, ly.hc2)
+            if tap is not None:  # observers want the streams' sum after every run
+                total = torch.empty((T, W), dtype=torch.float32, device=dev)
+                self._stream_norm(None, total, x, pending, None, None, s)
+                pending = None
+                tap(run, total)
+        total = torch.empty((T, W), dtype=torch.float32, device=dev)
+        self._stream_norm(None, total, x, pending, None, None, s)
+        return total
+
     def logits(self, x_rows: torch.Tensor) -> torch.Tensor:
         """Final norm and vocabulary projection of the given stream rows -> fp32 [n, vocab]."""
         n, W = x_rows.shape
         x_rows = x_rows.contiguous()
         h = torch.empty((n, W), dtype=self.dtype, device=self.device)
+        if self.cfg.block == "sequential":
+            check(lib.qs_hyb_stream_norm(h.data_ptr(), None, x_rows.data_ptr(), 1, None, 0, None, None, None, self.final_norm.data_ptr(),
+                                         self.cfg.norm_groups, self.cfg.norm_offset, self.cfg.eps, n, W, self.dt, _stream(self.device)))
+            return torch.mm(h, self.head.t()).float()
         check(lib.qs_hyb_rms_norm(h.data_ptr(), None, x_rows.data_ptr(), None, self.final_norm.data_ptr(), None, self.cfg.norm_offset, self.cfg.eps, n, W,
                                   self.dt, _stream(self.device)))
         return torch.mm(h, self.head.t()).float()

@@ -43,13 +43,15 @@ from typing import Callable, Dict, Optional, Tuple
 
 @dataclass(frozen=True)
 class RotaryConfig:
-    """Interleaved rotary embedding on the first `dims` entries of a head; optional YaRN blend of the frequencies."""
+    """Rotary embedding on the first `dims` entries of a head; optional YaRN blend of the frequencies.  layout "interleaved" pairs entries
+    (2i, 2i+1), "half" pairs entry i with entry i + dims/2."""
     dims: int
     base: float
     factor: Optional[float] = None   # None: no scaling
     original: float = 0.0
     fast: float = 0.0
     slow: float = 0.0
+    layout: str = "interleaved"
 
     def inv_freq(self):
         """Per-pair angular frequency (float64 list).  With scaling, pair i is blended between f_i and f_i / factor by a linear ramp whose
@@ -78,11 +80,48 @@ class AttentionMixerConfig:
     kv_heads: int
     dim: int
     vdim: int
-    rot: RotaryConfig
+    rot: Optional[RotaryConfig]  # None: positions do not enter the scores
     scale: float
     maps: int = 1
     diff: float = 0.0        # differential attention: offset of lambda, and (1 - diff) scales the normalised head output
     head_norm: bool = False  # unit-RMS per head after the maps are combined
+    # one map per head only:
+    bias: bool = False       # q / k / v projections have biases (tensors q.b, k.b, v.b)
+    qk_norm: bool = False    # q and k are brought to unit RMS per head before the scores
+    head_temp: bool = False  # scores of head h are multiplied by the learned number temp[h]
+    sink: bool = False       # the softmax denominator has one more term exp(sink[h]) without a value
+    chunk: int = 0           # > 0: a query sees only keys of its own chunk of this many positions (counted from position 0)
+    window: int = 0          # > 0: a query sees at most this many latest positions, its own included
+
+
+@dataclass(frozen=True)
+class GateRecurrenceMixerConfig:
+    """HGRN2: per head a [dim, vdim] fp32 state, S <- diag(f) S + (1 - f) v^T with a forget gate f per row that never falls below a learned
+    floor, read out with q = silu(.), unit RMS per head with a gain."""
+    heads: int
+    dim: int
+    vdim: int
+
+
+@dataclass(frozen=True)
+class RetentionMixerConfig:
+    """Retention: per head a [dim, vdim] fp32 state, S <- decay_h S + k v^T, o = S^T q; rotary q / k, k scaled by dim^-1/2; unit-RMS heads
+    times silu of an output gate."""
+    heads: int
+    dim: int
+    vdim: int
+    rot: Optional[RotaryConfig]
+    decay: Tuple[float, ...]
+    gated: bool = True
+
+
+@dataclass(frozen=True)
+class ParallelMixerConfig:
+    """Two mixers side by side on the same input (tensors under left.* / right.*); each output is RMS-normed over the width with its own gain
+    (left.out / right.out), the result is `scale` times their sum."""
+    left: object
+    right: object
+    scale: float = 0.5
 
 
 @dataclass(frozen=True)
@@ -100,6 +139,21 @@ class DeltaMixerConfig:
 class MlpConfig:
     kind: str
     ff: int
+
+
+@dataclass(frozen=True)
+class MoeConfig:
+    """Mixture of experts: softmax router over `experts`, the `top` best run, weighted by their scores as they are; experts compute
+    W_down(g sigmoid(alpha g) (u + 1)) with g = min(W_gate h, limit), u = clamp(W_up h, -limit, limit); optionally a shared expert for every
+    token with its own size and limit."""
+    experts: int
+    top: int
+    ff: int
+    limit: float
+    shared_ff: int = 0
+    shared_limit: float = 0.0
+    alpha: float = 1.702
+    kind: str = "moe"
 
 
 @dataclass(frozen=True)
@@ -123,6 +177,10 @@ class HybridConfig:
     pair_mul_prev: int = 0
     pair_mul_cur: int = 0
     norm_offset: float = 1.0  # gains are stored as offsets from this value
+    block: str = "parallel"   # "parallel": x += mixer(norm1 x) + ff(norm2 x);  "sequential": x += mixer(norm1 x), then x += ff(norm2 x)
+    streams: int = 0          # sequential blocks: > 0 = that many residual streams with hyper-connection coefficients (tensors hc1.*, hc2.*)
+    norm_groups: int = 1      # RMS norms work on this many equal consecutive parts of the width, each with its own statistic
+    embed_scale: float = 1.0
 
     def schedule(self):
         """Layer index of every layer RUN: layers loop_start .. loop_stop-1 run loop_times times in a row (same weights, own cache / state)."""
@@ -161,8 +219,45 @@ def parse_rizurax(c: dict) -> HybridConfig:
                         int(bg.get("buckets", 0)), int(bg.get("mul_prev", 0)), int(bg.get("mul_cur", 0)))
 
 
+def parse_toderax(c: dict) -> HybridConfig:
+    """Toderax: sequential blocks on `streams` residual streams (hyper-connections), group-wise RMS norms with plain gains, a scaled
+    embedding; mixers `hgrn2` (gate recurrence) and `parallel` (chunked softmax attention with a sink beside retention); mixture-of-experts
+    feed-forward with a shared expert."""
+    layers = []
+    for ly in c["layers"]:
+        m = ly["mixer"]
+        if ly["type"] == "hgrn2":
+            mixer = GateRecurrenceMixerConfig(int(m["heads"]), int(m["dim"]), int(m["vdim"]))
+        elif ly["type"] == "parallel":
+            a, r = m["left"], m["right"]
+            left = AttentionMixerConfig(int(a["heads"]), int(a["kv_heads"]), int(a["dim"]), int(a["vdim"]), None, float(a["scale"]), bias=True,
+                                        qk_norm=True, head_temp=True, sink=True, chunk=int((a.get("mask") or {}).get("size", 0)))
+            rot = r.get("rot")
+            right = RetentionMixerConfig(int(r["heads"]), int(r["dim"]), int(r["vdim"]),
+                                         RotaryConfig(int(rot["dims"]), float(rot["base"]), layout="half") if rot else None,
+                                         tuple(float(d) for d in r["decay"]))
+            if len(right.decay) != right.heads:
+                raise ValueError("retention needs one decay per head")
+            mixer = ParallelMixerConfig(left, right)
+        else:
+            raise ValueError(f"unknown mixer type {ly['type']!r}")
+        mlp = ly.get("mlp")
+        ff = None
+        if mlp is not None:
+            if mlp.get("kind") != "moe":
+                raise ValueError(f"unknown feed-forward kind {mlp.get('kind')!r}")
+            sh = mlp.get("shared") or {}
+            ff = MoeConfig(int(mlp["router"]["experts"]), int(mlp["router"]["top"]), int(mlp["expert"]["ff"]), float(mlp["expert"]["limit"]),
+                           int(sh.get("ff", 0)), float(sh.get("limit", 0.0)))
+        layers.append(HybridLayerConfig(ly["type"], mixer, ff))
+    norm = c["norm"]
+    return HybridConfig("Toderax", int(c["vocab"]), int(c["width"]), float(norm["eps"]), tuple(layers), norm_offset=0.0, block="sequential",
+                        streams=int(c.get("streams", 0)), norm_groups=int(norm.get("groups", 1)),
+                        embed_scale=float((c.get("embedding") or {}).get("scale", 1.0)))
+
+
 # config.json "architecture" -> parser.  The quantised Llama-family models of MODELS are built by qserve_b200.decode.DecodeRunner.
-ARCHITECTURES: Dict[str, Callable[[dict], HybridConfig]] = {"Rizurax": parse_rizurax}
+ARCHITECTURES: Dict[str, Callable[[dict], HybridConfig]] = {"Rizurax": parse_rizurax, "Toderax": parse_toderax}
 
 
 def read_model_config(model_dir: str) -> HybridConfig:
