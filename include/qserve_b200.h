@@ -250,8 +250,8 @@ QS_API int qs_hyb_attention_fast(void* out, int64_t out_stride, const void* q, i
                                  const int32_t* tile_entry, const int32_t* tile_row0, int n_tiles, const int32_t* long_tokens, int n_long,
                                  const int32_t* short_tokens, int n_short, const int32_t* entry_start, const int32_t* entry_len,
                                  const int32_t* entry_slot, const int32_t* entry_pos0, float* scratch, int heads, int kv_heads, int maps, int dim,
-                                 int vdim, float scale, float lambda, float out_scale, float eps, int head_norm, int page_size, int dtype,
-                                 void* stream);
+                                 int vdim, float scale, float lambda, float out_scale, float eps, int head_norm, int page_size, int chunk,
+                                 int window, const float* sinks, int dtype, void* stream);
 /* gated delta rule over projection rows [G*dim q | G*dim k | H*vdim v | H*vdim gate | H b | H a]: short convolution (taps) + silu on
  * q | k | v, unit q (times dim^-1/2) and k, beta = sigmoid(b), decay = exp(-exp(a_log) softplus(a + dt_bias)), then per head
  * S <- decay S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q; out = o * rsqrt(mean(o^2) + eps) * norm_w * silu(gate).
@@ -305,6 +305,17 @@ QS_API int qs_hyb_moe_router(float* route, int32_t* top_idx, float* top_w, const
  * limit_shared.  out [tokens, F]. */
 QS_API int qs_hyb_moe_act(void* out, const void* in, const float* route, int tokens_n, int experts, int ff, float limit, int ff_shared,
                           float limit_shared, float alpha, int dtype, void* stream);
+/* Expert-sorted rows of a mixture of experts.  Entry i = token * top + choice of top_idx [tokens, top]; the sorted order holds expert 0's
+ * entries first, then expert 1's, ..., each in token order.  row_of [tokens * top]: the entry's sorted row; src_token [tokens * top]: the token of
+ * a sorted row; ends [experts]: one past the last row of each expert.  work: int32, qs_hyb_moe_plan_work_ints(experts) elements. */
+QS_API int qs_hyb_moe_plan(int32_t* ends, int32_t* row_of, int32_t* src_token, int32_t* work, const int32_t* top_idx, int tokens_n, int experts,
+                           int top, void* stream);
+QS_API int64_t qs_hyb_moe_plan_work_ints(int experts);
+/* xs[row] = h[src_token[row]] (storage type rows of `width`) */
+QS_API int qs_hyb_moe_gather(void* xs, const void* h, const int32_t* src_token, int rows, int width, int dtype, void* stream);
+/* y[t] = shared[t] + sum_k top_w[t, k] rows[row_of[t * top + k]]; y fp32 [tokens, width]; rows, shared (may be NULL) storage type */
+QS_API int qs_hyb_moe_combine(float* y, const void* rows, const void* shared, const int32_t* row_of, const float* top_w, int tokens_n, int top,
+                              int width, int dtype, void* stream);
 
 #ifdef __cplusplus
 }

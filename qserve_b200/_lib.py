@@ -60,7 +60,7 @@ SIGNATURES = {
     "qs_hyb_attention_fast_supported": (c_int, [_I, _I, _I, _I, _I, _I, _L]),
     "qs_hyb_attention_scratch_floats": (_L, [_I, _I, _I, _I, _I]),
     "qs_hyb_attention_fast": (c_int, [_P, _L, _P, _L, _P, _P, _P, _P, _P, _I, _P, _P, _I, _P, _I, _P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I,
-                                      _F, _F, _F, _F, _I, _I, _I, _P]),
+                                      _F, _F, _F, _F, _I, _I, _I, _I, _P, _I, _P]),
     "qs_hyb_gated_delta": (c_int, [_P, _L, _P, _P, _P, _L, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _F, _I, _P]),
     # csrc/hybrid_blocks.cu, csrc/hybrid_linear.cu
     "qs_hyb_stream_norm": (c_int, [_P, _P, _P, _I, _P, _I, _P, _P, _P, _P, _I, _F, _F, _I, _I, _I, _P]),
@@ -70,6 +70,10 @@ SIGNATURES = {
     "qs_hyb_retention": (c_int, [_P, _L, _P, _P, _P, _L, _P, _P, _I, _F, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P]),
     "qs_hyb_moe_router": (c_int, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P]),
     "qs_hyb_moe_act": (c_int, [_P, _P, _P, _I, _I, _I, _F, _I, _F, _F, _I, _P]),
+    "qs_hyb_moe_plan": (c_int, [_P, _P, _P, _P, _P, _I, _I, _I, _P]),
+    "qs_hyb_moe_plan_work_ints": (_L, [_I]),
+    "qs_hyb_moe_gather": (c_int, [_P, _P, _P, _I, _I, _I, _P]),
+    "qs_hyb_moe_combine": (c_int, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _P]),
 }
 
 ABI_VERSION = 1

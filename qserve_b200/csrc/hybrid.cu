@@ -370,7 +370,8 @@ __global__ void __launch_bounds__(128, KT == 32 ? 3 : 2) tile_attention_kernel(
     float* __restrict__ a_out, const __nv_bfloat16* __restrict__ q, long long q_stride, const __nv_bfloat16* __restrict__ kpool,
     const __nv_bfloat16* __restrict__ vpool, const int* __restrict__ tile_entry, const int* __restrict__ tile_row0,
     const int* __restrict__ entry_start, const int* __restrict__ entry_len, const int* __restrict__ entry_slot, const int* __restrict__ entry_pos0,
-    const int* __restrict__ block_table, int max_blocks, int H, int G, int maps, int D, float scale, int page) {
+    const int* __restrict__ block_table, int max_blocks, int H, int G, int maps, int D, float scale, int page, int chunk, int window,
+    const float* __restrict__ sinks) {
   extern __shared__ __align__(16) unsigned char smraw[];
   constexpr int Dv = NVT * 16;
   const int SD = D + kPad, SV = Dv + kPad;
@@ -393,11 +394,17 @@ __global__ void __launch_bounds__(128, KT == 32 ? 3 : 2) tile_attention_kernel(
   float o[2 * NVT][4];
 #pragma unroll
   for (int i = 0; i < 2 * NVT; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
-  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
   const int last_qpos = qpos0 + n_rows - 1;
   const int n_kt = last_qpos / KT + 1;
+  const int kt_lo = first_key(qpos0, chunk, window) / KT;  // the tile's first row sees furthest back
   const float scale_log2 = scale * 1.4426950408889634f;
   const int qrow = warp * 16 + (lane >> 2);  // this thread's rows: qrow, qrow + 8
+  const int fk[2] = {first_key(qpos0 + qrow, chunk, window), first_key(qpos0 + qrow + 8, chunk, window)};
+  const int warp_fk = first_key(min(last_qpos, qpos0 + warp * 16 + 15), chunk, window);  // the largest first key among the warp's rows
+  // a sink is one more term of the denominator without a value: the running maximum starts from it and one lane of the row's quad carries its 1
+  const float sink2 = sinks != nullptr ? sinks[h] * 1.4426950408889634f : -INFINITY;
+  const float l0 = sinks != nullptr && (lane & 3) == 0 ? 1.f : 0.f;
+  float m_run[2] = {sink2, sink2}, l_run[2] = {l0, l0};
   // key / value tiles are double-buffered: tile kt + 1 streams in with cp.async while tile kt is multiplied
   constexpr int TPR = 128 / KT;
   // TPR threads per key row, alternating 16-byte chunks: one block-table lookup per thread and tile, made one tile ahead of its use so
@@ -423,9 +430,9 @@ __global__ void __launch_bounds__(128, KT == 32 ? 3 : 2) tile_attention_kernel(
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
   };
-  load_kv(0, 0, cell_of(0));
-  long long cell_next = n_kt > 1 ? cell_of(1) : -1;
-  for (int kt = 0; kt < n_kt; ++kt) {
+  load_kv(kt_lo, kt_lo & 1, cell_of(kt_lo));
+  long long cell_next = kt_lo + 1 < n_kt ? cell_of(kt_lo + 1) : -1;
+  for (int kt = kt_lo; kt < n_kt; ++kt) {
     if (kt + 1 < n_kt) {
       load_kv(kt + 1, (kt + 1) & 1, cell_next);
       if (kt + 2 < n_kt) cell_next = cell_of(kt + 2);
@@ -452,16 +459,16 @@ __global__ void __launch_bounds__(128, KT == 32 ? 3 : 2) tile_attention_kernel(
     }
     // scale, causal mask, online softmax (rows qrow and qrow + 8; a row's columns live in the 4 lanes of a quad)
     float mx[2] = {-INFINITY, -INFINITY};
-    const bool diagonal = kt * KT + KT - 1 > qpos0 + warp * 16;
+    const bool diagonal = kt * KT + KT - 1 > qpos0 + warp * 16 || kt * KT < warp_fk;
 #pragma unroll
     for (int nt = 0; nt < KT / 8; ++nt)
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         float v = s[nt][j] * scale_log2;
-        if (diagonal) {  // warp-uniform: only tiles that reach past this warp's first row need the causal mask
+        if (diagonal) {  // warp-uniform: only tiles that reach past this warp's first row, or start before a row's first key, need a mask
           const int kpos = kt * KT + nt * 8 + (lane & 3) * 2 + (j & 1);
           const int qp = qpos0 + qrow + (j >> 1) * 8;
-          if (kpos > qp) v = -INFINITY;
+          if (kpos > qp || kpos < fk[j >> 1]) v = -INFINITY;
         }
         s[nt][j] = v;
         mx[j >> 1] = fmaxf(mx[j >> 1], v);
@@ -567,7 +574,7 @@ template <int NVT, int PSPLIT>
 __global__ void __launch_bounds__(128) group_attention_kernel(
     float* __restrict__ part, const __nv_bfloat16* __restrict__ q, long long q_stride, const __nv_bfloat16* __restrict__ kpool,
     const __nv_bfloat16* __restrict__ vpool, const int* __restrict__ tok_list, const int* __restrict__ tok_slot, const int* __restrict__ tok_pos,
-    const int* __restrict__ block_table, int max_blocks, int H, int G, int maps, int D, float scale, int page, int shares) {
+    const int* __restrict__ block_table, int max_blocks, int H, int G, int maps, int D, float scale, int page, int shares, int chunk, int window) {
   extern __shared__ __align__(16) unsigned char smraw[];
   constexpr int Dv = NVT * 16;
   const int SD = D + kPad, SV = Dv + kPad, R = H / G;
@@ -579,8 +586,9 @@ __global__ void __launch_bounds__(128) group_attention_kernel(
   const int* bt = block_table + (size_t)tok_slot[t] * max_blocks;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int dch = D >> 3;
-  const int n_kt = pos / kTileK + 1, per = (n_kt + shares - 1) / shares;
-  const int kt0 = share * per, kt1 = min(n_kt, kt0 + per);
+  const int first = first_key(pos, chunk, window), kt_lo = first / kTileK;
+  const int n_kt = pos / kTileK + 1, per = (n_kt - kt_lo + shares - 1) / shares;
+  const int kt0 = kt_lo + share * per, kt1 = min(n_kt, kt0 + per);
   float* pout = part + ((((size_t)li * H + g * R) * maps + m) * shares + share) * (size_t)(2 + Dv);  // head g R + r: + r maps shares (2 + Dv)
   const size_t head_step = (size_t)maps * shares * (2 + Dv);
   if (kt0 >= kt1) {  // a share without keys weighs nothing in the merge
@@ -651,7 +659,7 @@ __global__ void __launch_bounds__(128) group_attention_kernel(
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         const int kpos = kt * kTileK + warp * 16 + nt * 8 + (lane & 3) * 2 + (j & 1);
-        const float v = kpos <= pos ? s[nt][j] * scale_log2 : -INFINITY;
+        const float v = kpos <= pos && kpos >= first ? s[nt][j] * scale_log2 : -INFINITY;
         s[nt][j] = v;
         mx[j >> 1] = fmaxf(mx[j >> 1], v);
       }
@@ -744,7 +752,8 @@ __global__ void __launch_bounds__(128) group_attention_kernel(
 // merge the shares of every (listed token, head, map), then finish the head as multimap_combine_kernel does.  One warp per (token, head).
 template <typename ST>
 __global__ void group_merge_kernel(ST* __restrict__ out, long long out_stride, const float* __restrict__ part, const int* __restrict__ tok_list,
-                                   int n_list, int H, int maps, int Dv, int shares, float lambda, float out_scale, float eps, int head_norm) {
+                                   int n_list, int H, int maps, int Dv, int shares, float lambda, float out_scale, float eps, int head_norm,
+                                   const float* __restrict__ sinks) {
   const int w = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
   if (w >= n_list * H) return;
   const int li = w / H, h = w - li * H, t = tok_list[li];
@@ -755,9 +764,10 @@ __global__ void group_merge_kernel(ST* __restrict__ out, long long out_stride, c
   for (int j = 0; j < 8; ++j) ov[j] = 0.f;
   for (int mm = 0; mm < maps; ++mm) {
     const float* pm = base + (size_t)mm * shares * (2 + Dv);
-    float M = -INFINITY;
+    const float sink2 = sinks != nullptr ? sinks[h] * 1.4426950408889634f : -INFINITY;  // the sink: a share of maximum sink, sum 1, no output
+    float M = sink2;
     for (int z = 0; z < shares; ++z) M = fmaxf(M, pm[(size_t)z * (2 + Dv)]);
-    float den = 0.f, num[8];
+    float den = sinks != nullptr ? fast_exp2(sink2 - M) : 0.f, num[8];
 #pragma unroll
     for (int j = 0; j < 8; ++j) num[j] = 0.f;
     for (int z = 0; z < shares; ++z) {
@@ -1084,7 +1094,7 @@ constexpr int kTileKeysPrompt = 32;
 template <int NVT, int KT>
 int launch_tiles(float* scratch, const void* q, long long q_stride, const void* kpool, const void* vpool, const int* tile_entry, const int* tile_row0,
                  int n_tiles, const int* entry_start, const int* entry_len, const int* entry_slot, const int* entry_pos0, const int* block_table,
-                 int max_blocks, int H, int G, int maps, int D, float scale, int page, cudaStream_t s) {
+                 int max_blocks, int H, int G, int maps, int D, float scale, int page, int chunk, int window, const float* sinks, cudaStream_t s) {
   const size_t smem = ((size_t)(kTileQ + 2 * KT) * (D + kPad) + (size_t)2 * KT * (NVT * 16 + kPad)) * sizeof(__nv_bfloat16);
   static bool attr_set[kMaxDevices] = {};
   if (smem > 48 * 1024 && !attr_set[device_ordinal()]) {
@@ -1092,7 +1102,7 @@ int launch_tiles(float* scratch, const void* q, long long q_stride, const void* 
     attr_set[device_ordinal()] = true;
   }
   tile_attention_kernel<NVT, 3, KT><<<dim3(n_tiles, H * maps), 128, smem, s>>>(scratch, (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)kpool,
-      (const __nv_bfloat16*)vpool, tile_entry, tile_row0, entry_start, entry_len, entry_slot, entry_pos0, block_table, max_blocks, H, G, maps, D, scale, page);
+      (const __nv_bfloat16*)vpool, tile_entry, tile_row0, entry_start, entry_len, entry_slot, entry_pos0, block_table, max_blocks, H, G, maps, D, scale, page, chunk, window, sinks);
   return check_cuda(cudaGetLastError(), "hyb_attention tiles");
 }
 
@@ -1106,7 +1116,8 @@ inline int group_shares(int n_tokens, int G, int maps) {
 template <int NVT>
 int launch_group(void* out, long long out_stride, float* part, const void* q, long long q_stride, const void* kpool, const void* vpool,
                  const int* tok_list, int n_list, const int* tok_slot, const int* tok_pos, const int* block_table, int max_blocks, int H, int G,
-                 int maps, int D, float scale, float lambda, float out_scale, float eps, int head_norm, int page, cudaStream_t s) {
+                 int maps, int D, float scale, float lambda, float out_scale, float eps, int head_norm, int page, int chunk, int window,
+                 const float* sinks, cudaStream_t s) {
   const size_t smem = ((size_t)(16 + 2 * kTileK) * (D + kPad) + (size_t)2 * kTileK * (NVT * 16 + kPad)) * sizeof(__nv_bfloat16);
   static bool attr_set[kMaxDevices] = {};
   if (smem > 48 * 1024 && !attr_set[device_ordinal()]) {
@@ -1115,10 +1126,10 @@ int launch_group(void* out, long long out_stride, float* part, const void* q, lo
   }
   const int shares = group_shares(n_list, G, maps);
   group_attention_kernel<NVT, 3><<<dim3(n_list, G * maps, shares), 128, smem, s>>>(part, (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)kpool,
-      (const __nv_bfloat16*)vpool, tok_list, tok_slot, tok_pos, block_table, max_blocks, H, G, maps, D, scale, page, shares);
+      (const __nv_bfloat16*)vpool, tok_list, tok_slot, tok_pos, block_table, max_blocks, H, G, maps, D, scale, page, shares, chunk, window);
   const int warps = n_list * H;
   group_merge_kernel<__nv_bfloat16><<<(warps + 3) / 4, 128, 0, s>>>((__nv_bfloat16*)out, out_stride, part, tok_list, n_list, H, maps, NVT * 16, shares,
-                                                                     lambda, out_scale, eps, head_norm);
+                                                                     lambda, out_scale, eps, head_norm, sinks);
   return check_cuda(cudaGetLastError(), "hyb_attention single tokens");
 }
 
@@ -1282,7 +1293,8 @@ int qs_hyb_attention_fast(void* out, int64_t out_stride, const void* q, int64_t 
                           const int32_t* tile_row0, int n_tiles, const int32_t* long_tokens, int n_long, const int32_t* short_tokens, int n_short,
                           const int32_t* entry_start, const int32_t* entry_len, const int32_t* entry_slot, const int32_t* entry_pos0,
                           float* scratch, int heads, int kv_heads, int maps, int dim, int vdim, float scale, float lambda, float out_scale, float eps,
-                          int head_norm, int page_size, int dtype, void* stream) {
+                          int head_norm, int page_size, int chunk, int window, const float* sinks, int dtype, void* stream) {
+  QS_REQUIRE(chunk >= 0 && window >= 0, "hyb_attention_fast: negative chunk or window");
   QS_REQUIRE(out && q && kpool && vpool && tok_slot && tok_pos && block_table, "hyb_attention_fast: null tensor");
   QS_REQUIRE(fast_attention_supported(dtype, heads, kv_heads, maps, dim, vdim, q_stride), "hyb_attention_fast: shape not supported (use qs_hyb_attention)");
   QS_REQUIRE(n_tiles == 0 || (tile_entry && tile_row0 && long_tokens && scratch && entry_start && entry_len && entry_slot && entry_pos0),
@@ -1292,7 +1304,7 @@ int qs_hyb_attention_fast(void* out, int64_t out_stride, const void* q, int64_t 
   if (n_tiles > 0) {
     int rc = 0;
 #define QS_TILES(NVT, KT) rc = launch_tiles<NVT, KT>(scratch, q, q_stride, kpool, vpool, tile_entry, tile_row0, n_tiles, entry_start, entry_len, entry_slot, \
-                                             entry_pos0, block_table, max_blocks, heads, kv_heads, maps, dim, scale, page_size, s)
+                                             entry_pos0, block_table, max_blocks, heads, kv_heads, maps, dim, scale, page_size, chunk, window, sinks, s)
     switch (vdim / 16) {
       case 2: QS_TILES(2, kTileKeysPrompt); break;
       case 4: QS_TILES(4, kTileKeysPrompt); break;
@@ -1310,7 +1322,7 @@ int qs_hyb_attention_fast(void* out, int64_t out_stride, const void* q, int64_t 
     int rc = 0;
     float* part = scratch + (size_t)(n_long + n_short) * heads * maps * vdim;  // behind the per-map outputs of the tiles
 #define QS_GROUP(NVT) rc = launch_group<NVT>(out, out_stride, part, q, q_stride, kpool, vpool, short_tokens, n_short, tok_slot, tok_pos, block_table, \
-                                             max_blocks, heads, kv_heads, maps, dim, scale, lambda, out_scale, eps, head_norm, page_size, s)
+                                             max_blocks, heads, kv_heads, maps, dim, scale, lambda, out_scale, eps, head_norm, page_size, chunk, window, sinks, s)
     switch (vdim / 16) {
       case 2: QS_GROUP(2); break;
       case 4: QS_GROUP(4); break;

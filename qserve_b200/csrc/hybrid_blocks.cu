@@ -260,6 +260,90 @@ __global__ void moe_act_kernel(ST* __restrict__ out, const ST* __restrict__ in, 
   stf(out + (size_t)t * F + j, y);
 }
 
+// ---------------------------------------------------------------------------------------------------------------------------------
+// Expert-sorted rows.  Entry i = token * top + choice of top_idx names an expert; the entries of expert 0 come first, then expert 1's, ...,
+// each expert's in token order (so the order never depends on timing).  Two kernels, one block per expert:
+//   count: how many entries of the expert each thread's contiguous chunk of entries holds, and their sum
+//   place: row_of[i] = the entry's row in the sorted order, src_token[row] = its token, ends[e] = one past the expert's last row
+// ---------------------------------------------------------------------------------------------------------------------------------
+constexpr int kPlanThreads = 256;
+
+__global__ void __launch_bounds__(kPlanThreads) moe_count_kernel(int* __restrict__ counts, int* __restrict__ chunk_counts,
+                                                                 const int* __restrict__ top_idx, int n) {
+  __shared__ int red[kPlanThreads / 32];
+  const int e = blockIdx.x, tid = threadIdx.x;
+  const int per = (n + kPlanThreads - 1) / kPlanThreads, lo = tid * per, hi = min(n, lo + per);
+  int c = 0;
+  for (int i = lo; i < hi; ++i) c += top_idx[i] == e;
+  chunk_counts[e * kPlanThreads + tid] = c;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) c += __shfl_xor_sync(0xffffffffu, c, o);
+  if ((tid & 31) == 0) red[tid >> 5] = c;
+  __syncthreads();
+  if (tid == 0) {
+    int t = 0;
+    for (int w = 0; w < kPlanThreads / 32; ++w) t += red[w];
+    counts[e] = t;
+  }
+}
+
+__global__ void __launch_bounds__(kPlanThreads) moe_place_kernel(int* __restrict__ ends, int* __restrict__ row_of, int* __restrict__ src_token,
+                                                                 const int* __restrict__ counts, const int* __restrict__ chunk_counts,
+                                                                 const int* __restrict__ top_idx, int n, int top) {
+  __shared__ int scan[kPlanThreads];
+  __shared__ int base_s;
+  const int e = blockIdx.x, tid = threadIdx.x;
+  const int mine = chunk_counts[e * kPlanThreads + tid];
+  scan[tid] = mine;
+  if (tid == 0) {
+    int b = 0;
+    for (int i = 0; i < e; ++i) b += counts[i];
+    base_s = b;
+    ends[e] = b + counts[e];
+  }
+  __syncthreads();
+  for (int o = 1; o < kPlanThreads; o <<= 1) {  // inclusive scan of the chunks' counts
+    const int v = tid >= o ? scan[tid - o] : 0;
+    __syncthreads();
+    scan[tid] += v;
+    __syncthreads();
+  }
+  int pos = base_s + scan[tid] - mine;
+  const int per = (n + kPlanThreads - 1) / kPlanThreads, lo = tid * per, hi = min(n, lo + per);
+  for (int i = lo; i < hi; ++i)
+    if (top_idx[i] == e) {
+      row_of[i] = pos;
+      src_token[pos] = i / top;
+      ++pos;
+    }
+}
+
+// xs[row] = h[src_token[row]]
+template <typename ST>
+__global__ void moe_gather_kernel(ST* __restrict__ xs, const ST* __restrict__ h, const int* __restrict__ src_token, int W, int vec) {
+  const size_t r = blockIdx.x, t = src_token[r];
+  if (vec) {
+    const int n16 = W * (int)sizeof(ST) / 16;
+    const uint4* src = reinterpret_cast<const uint4*>(h + t * W);
+    uint4* dst = reinterpret_cast<uint4*>(xs + r * W);
+    for (int i = threadIdx.x; i < n16; i += blockDim.x) dst[i] = src[i];
+  } else {
+    for (int i = threadIdx.x; i < W; i += blockDim.x) xs[r * W + i] = h[t * W + i];
+  }
+}
+
+// y[t] = shared[t] + sum_k top_w[t][k] * rows[row_of[t * top + k]]   (fp32 sums in the order of k; y fp32; shared may be null)
+template <typename ST>
+__global__ void moe_combine_kernel(float* __restrict__ y, const ST* __restrict__ rows, const ST* __restrict__ shared, const int* __restrict__ row_of,
+                                   const float* __restrict__ top_w, int top, int W) {
+  const size_t t = blockIdx.x;
+  for (int i = threadIdx.x; i < W; i += blockDim.x) {
+    float a = shared != nullptr ? ldf(shared + t * W + i) : 0.f;
+    for (int k = 0; k < top; ++k) a += top_w[t * top + k] * ldf(rows + (size_t)row_of[t * top + k] * W + i);
+    y[t * W + i] = a;
+  }
+}
+
 }  // namespace
 }  // namespace qs
 
@@ -362,6 +446,44 @@ int qs_hyb_moe_act(void* out, const void* in, const float* route, int tokens_n, 
                                                              limit_shared, alpha)),
         (moe_act_kernel<float><<<grid, 256, 0, s>>>((float*)out, (const float*)in, route, experts, ff, limit, ff_shared, limit_shared, alpha)));
   return check_cuda(cudaGetLastError(), "hyb_moe_act");
+}
+
+int qs_hyb_moe_plan(int32_t* ends, int32_t* row_of, int32_t* src_token, int32_t* work, const int32_t* top_idx, int tokens_n, int experts, int top,
+                    void* stream) {
+  QS_REQUIRE(ends && row_of && src_token && work && top_idx, "hyb_moe_plan: null tensor");
+  QS_REQUIRE(experts >= 1 && top >= 1 && top <= experts, "hyb_moe_plan: 1 <= top <= experts");
+  if (tokens_n == 0) return qs::QS_OK;
+  cudaStream_t s = (cudaStream_t)stream;
+  int* counts = work;                 // [experts]
+  int* chunk_counts = work + experts;  // [experts][kPlanThreads]
+  moe_count_kernel<<<experts, kPlanThreads, 0, s>>>(counts, chunk_counts, top_idx, tokens_n * top);
+  moe_place_kernel<<<experts, kPlanThreads, 0, s>>>(ends, row_of, src_token, counts, chunk_counts, top_idx, tokens_n * top, top);
+  return check_cuda(cudaGetLastError(), "hyb_moe_plan");
+}
+
+int64_t qs_hyb_moe_plan_work_ints(int experts) { return (int64_t)experts * (1 + kPlanThreads); }
+
+int qs_hyb_moe_gather(void* xs, const void* h, const int32_t* src_token, int rows, int width, int dtype, void* stream) {
+  QS_REQUIRE(xs && h && src_token, "hyb_moe_gather: null tensor");
+  if (rows == 0) return qs::QS_OK;
+  cudaStream_t s = (cudaStream_t)stream;
+  const size_t es = dtype == QS_DTYPE_BF16 ? 2 : 4;
+  const int vec = (width * es) % 16 == 0 && (reinterpret_cast<uintptr_t>(xs) & 15) == 0 && (reinterpret_cast<uintptr_t>(h) & 15) == 0;
+  QS_DT(dtype, (moe_gather_kernel<__nv_bfloat16><<<rows, 128, 0, s>>>((__nv_bfloat16*)xs, (const __nv_bfloat16*)h, src_token, width, vec)),
+        (moe_gather_kernel<float><<<rows, 128, 0, s>>>((float*)xs, (const float*)h, src_token, width, vec)));
+  return check_cuda(cudaGetLastError(), "hyb_moe_gather");
+}
+
+int qs_hyb_moe_combine(float* y, const void* rows, const void* shared, const int32_t* row_of, const float* top_w, int tokens_n, int top, int width,
+                       int dtype, void* stream) {
+  QS_REQUIRE(y && rows && row_of && top_w, "hyb_moe_combine: null tensor");
+  if (tokens_n == 0) return qs::QS_OK;
+  cudaStream_t s = (cudaStream_t)stream;
+  const int threads = width >= 1024 ? 256 : 128;
+  QS_DT(dtype,
+        (moe_combine_kernel<__nv_bfloat16><<<tokens_n, threads, 0, s>>>(y, (const __nv_bfloat16*)rows, (const __nv_bfloat16*)shared, row_of, top_w, top, width)),
+        (moe_combine_kernel<float><<<tokens_n, threads, 0, s>>>(y, (const float*)rows, (const float*)shared, row_of, top_w, top, width)));
+  return check_cuda(cudaGetLastError(), "hyb_moe_combine");
 }
 
 }  // extern "C"

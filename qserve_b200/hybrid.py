@@ -168,8 +168,7 @@ class MultiMapAttentionMixer(_Mixer):
 
     def run(self, proj: torch.Tensor, out: torch.Tensor, b: StepBatch, run_cache: dict, page_size: int, scratch, dt: int, stream) -> None:
         m = self.m
-        masked = m.chunk > 0 or m.window > 0 or m.sink
-        fast = not masked and scratch is not None and \
+        fast = scratch is not None and \
             lib.qs_hyb_attention_fast_supported(dt, m.heads, m.kv_heads, m.maps, m.dim, m.vdim, proj.stride(0)) == 1
         if self.general:
             check(lib.qs_hyb_qk_prepare_append(proj.data_ptr(), proj.stride(0), _p(self.bias), _p(self.temp), _p(b.tok_slot), _p(b.tok_pos),
@@ -188,7 +187,7 @@ class MultiMapAttentionMixer(_Mixer):
                                             _p(b.tile_entry), _p(b.tile_row0), b.n_tiles, _p(b.long_tokens), b.n_long, _p(b.short_tokens), b.n_short,
                                             _p(b.entry_start), _p(b.entry_len), _p(b.entry_slot), _p(b.entry_pos0), scratch.data_ptr(), m.heads,
                                             m.kv_heads, m.maps, m.dim, m.vdim, m.scale, self.lam, self.out_scale, self.eps,
-                                            1 if m.head_norm else 0, page_size, dt, stream))
+                                            1 if m.head_norm else 0, page_size, m.chunk, m.window, _p(self.sinks), dt, stream))
             return
         check(lib.qs_hyb_attention(out.data_ptr(), out.stride(0), proj.data_ptr(), proj.stride(0), run_cache["k"].data_ptr(),
                                    run_cache["v"].data_ptr(), _p(b.tok_slot), _p(b.tok_pos), _p(b.block_table), b.block_table.shape[1],
@@ -343,29 +342,51 @@ MIXERS = {AttentionMixerConfig: MultiMapAttentionMixer, DeltaMixerConfig: GatedD
 # ------------------------------------------------------------------------------------------------------------------------
 # feed-forwards of sequential blocks
 # ------------------------------------------------------------------------------------------------------------------------
+MOE_IMPL = None  # tests: force "sorted" or "dense"; None picks by storage type and sizes
+
+
 class MoeFeedForward:
-    """Mixture of experts with an optional shared expert as ONE pair of products: the gate / up rows of all experts (and the shared one) are
-    stacked, the activation kernel weights an expert's columns with the token's router score for it (exact zeros for experts the token does
-    not use), and the stacked down projection sums the weighted experts in its fp32 accumulation.  The router (fp32 logits, softmax, top
-    scores) is one kernel."""
+    """Mixture of experts with an optional shared expert.  The router (fp32 logits, softmax, top scores) is one kernel.  Two ways to run the
+    experts:
+
+    "sorted": the (token, chosen expert) pairs are sorted by expert on the device (every expert's rows in token order), the tokens' rows are
+              gathered in that order, two grouped matrix products (one group per expert) make gate | up and the down projection, and a kernel
+              sums a token's experts with their router scores in fp32, beside the shared expert's dense products.  Only chosen experts compute.
+    "dense":  the gate / up rows of all experts (and the shared one) are stacked into ONE pair of products; the activation kernel weights an
+              expert's columns with the token's router score for it (exact zeros for experts the token does not use), and the stacked down
+              projection sums the weighted experts in its fp32 accumulation.  Exact in every storage type and for every size.
+    bfloat16 models whose sizes suit the grouped product (width and expert size multiples of 8) run "sorted", all others "dense"."""
 
     def __init__(self, c: MoeConfig, w: Dict[str, torch.Tensor], width: int, dtype, device):
-        self.c = c
+        self.c, self.width = c, width
         st = lambda t: t.to(device=device, dtype=dtype).contiguous()
-        names = [f"e{e}" for e in range(c.experts)] + (["shared"] if c.shared_ff else [])
+        experts = [f"e{e}" for e in range(c.experts)]
+        names = experts + (["shared"] if c.shared_ff else [])
         for n in names:
             ff = c.shared_ff if n == "shared" else c.ff
             for part, shape in (("gate", (ff, width)), ("up", (ff, width)), ("down", (width, ff))):
                 if tuple(w[f"{n}.{part}"].shape) != shape:
                     raise ValueError(f"expert weight {n}.{part}: {tuple(w[f'{n}.{part}'].shape)} is not {shape}")
-        self.F = c.experts * c.ff + c.shared_ff
-        self.w_in = st(torch.cat([w[f"{n}.gate"] for n in names] + [w[f"{n}.up"] for n in names], 0))  # [2 F, W]
-        self.w_down = st(torch.cat([w[f"{n}.down"] for n in names], 1))                               # [W, F]
+        self.impl = MOE_IMPL or ("sorted" if dtype == torch.bfloat16 and width % 8 == 0 and c.ff % 8 == 0 else "dense")
+        if self.impl == "sorted":
+            self.w_gu = st(torch.stack([torch.cat([w[f"{n}.gate"], w[f"{n}.up"]], 0) for n in experts]))  # [E, 2 ff, W]
+            self.w_dn = st(torch.stack([w[f"{n}.down"] for n in experts]))                               # [E, W, ff]
+            if c.shared_ff:
+                self.w_sh_in = st(torch.cat([w["shared.gate"], w["shared.up"]], 0))
+                self.w_sh_dn = st(w["shared.down"])
+            self.work = torch.empty(int(lib.qs_hyb_moe_plan_work_ints(c.experts)), dtype=torch.int32, device=device)
+        elif self.impl == "dense":
+            self.F = c.experts * c.ff + c.shared_ff
+            self.w_in = st(torch.cat([w[f"{n}.gate"] for n in names] + [w[f"{n}.up"] for n in names], 0))  # [2 F, W]
+            self.w_down = st(torch.cat([w[f"{n}.down"] for n in names], 1))                               # [W, F]
+        else:
+            raise ValueError(f"unknown expert implementation {self.impl!r}")
         self.w_router = w["router"].to(torch.float32).to(device).contiguous()
         if tuple(self.w_router.shape) != (c.experts, width):
             raise ValueError("router weight is not [experts, width]")
 
-    def run(self, h: torch.Tensor, dt: int, stream) -> torch.Tensor:
+    def run(self, h: torch.Tensor, dt: int, stream):
+        """h [T, W] (storage type) -> (rows [T, W], rows are fp32)."""
         c, T, W = self.c, h.shape[0], h.shape[1]
         dev = h.device
         route = torch.empty((T, c.experts), dtype=torch.float32, device=dev)
@@ -373,11 +394,33 @@ class MoeFeedForward:
         top_w = torch.empty((T, c.top), dtype=torch.float32, device=dev)
         check(lib.qs_hyb_moe_router(route.data_ptr(), top_idx.data_ptr(), top_w.data_ptr(), h.data_ptr(), self.w_router.data_ptr(), T, W, c.experts,
                                     c.top, dt, stream))
-        gu = torch.mm(h, self.w_in.t())
-        act = torch.empty((T, self.F), dtype=h.dtype, device=dev)
-        check(lib.qs_hyb_moe_act(act.data_ptr(), gu.data_ptr(), route.data_ptr(), T, c.experts, c.ff, c.limit, c.shared_ff, c.shared_limit, c.alpha,
-                                 dt, stream))
-        return torch.mm(act, self.w_down.t())
+        if self.impl == "dense":
+            gu = torch.mm(h, self.w_in.t())
+            act = torch.empty((T, self.F), dtype=h.dtype, device=dev)
+            check(lib.qs_hyb_moe_act(act.data_ptr(), gu.data_ptr(), route.data_ptr(), T, c.experts, c.ff, c.limit, c.shared_ff, c.shared_limit, c.alpha,
+                                     dt, stream))
+            return torch.mm(act, self.w_down.t()), False
+        n = T * c.top
+        ends = torch.empty(c.experts, dtype=torch.int32, device=dev)
+        row_of = torch.empty(n, dtype=torch.int32, device=dev)
+        src = torch.empty(n, dtype=torch.int32, device=dev)
+        check(lib.qs_hyb_moe_plan(ends.data_ptr(), row_of.data_ptr(), src.data_ptr(), self.work.data_ptr(), top_idx.data_ptr(), T, c.experts, c.top,
+                                  stream))
+        xs = torch.empty((n, W), dtype=h.dtype, device=dev)
+        check(lib.qs_hyb_moe_gather(xs.data_ptr(), h.data_ptr(), src.data_ptr(), n, W, dt, stream))
+        gu = torch.nn.functional.grouped_mm(xs, self.w_gu.transpose(-2, -1), offs=ends)
+        act = torch.empty((n, c.ff), dtype=h.dtype, device=dev)
+        check(lib.qs_hyb_moe_act(act.data_ptr(), gu.data_ptr(), None, n, 0, 0, 0.0, c.ff, c.limit, c.alpha, dt, stream))
+        rows = torch.nn.functional.grouped_mm(act, self.w_dn.transpose(-2, -1), offs=ends)
+        shared = None
+        if c.shared_ff:
+            gs = torch.mm(h, self.w_sh_in.t())
+            sa = torch.empty((T, c.shared_ff), dtype=h.dtype, device=dev)
+            check(lib.qs_hyb_moe_act(sa.data_ptr(), gs.data_ptr(), None, T, 0, 0, 0.0, c.shared_ff, c.shared_limit, c.alpha, dt, stream))
+            shared = torch.mm(sa, self.w_sh_dn.t())
+        y = torch.empty((T, W), dtype=torch.float32, device=dev)
+        check(lib.qs_hyb_moe_combine(y.data_ptr(), rows.data_ptr(), _p(shared), row_of.data_ptr(), top_w.data_ptr(), T, c.top, W, dt, stream))
+        return y, True
 
 
 class DenseFeedForward:
@@ -388,11 +431,11 @@ class DenseFeedForward:
         self.ff = c.ff
         self.w_in, self.w_down = st(torch.cat([w["gate"], w["up"]], 0)), st(w["down"])
 
-    def run(self, h: torch.Tensor, dt: int, stream) -> torch.Tensor:
+    def run(self, h: torch.Tensor, dt: int, stream):
         gu = torch.mm(h, self.w_in.t())
         act = torch.empty((h.shape[0], self.ff), dtype=h.dtype, device=h.device)
         check(lib.qs_hyb_gelu_tanh_mul(act.data_ptr(), act.stride(0), gu.data_ptr(), h.shape[0], self.ff, dt, stream))
-        return torch.mm(act, self.w_down.t())
+        return torch.mm(act, self.w_down.t()), False
 
 
 FEED_FORWARDS = {MoeConfig: MoeFeedForward, MlpConfig: DenseFeedForward}
@@ -561,7 +604,7 @@ class HybridDecoder:
             pending = (y, y32, ly.hc1)
             if ly.ff is not None:
                 self._stream_norm(h, None, x, pending, ly.hc2.cin, ly.norm2, s)
-                pending = (ly.ff.run(h, dt, s), False, ly.hc2)
+                pending = (*ly.ff.run(h, dt, s), ly.hc2)
             if tap is not None:  # observers want the streams' sum after every run
                 total = torch.empty((T, W), dtype=torch.float32, device=dev)
                 self._stream_norm(None, total, x, pending, None, None, s)

@@ -135,6 +135,38 @@ def test_expert_mixture(dev, spec):
     assert row_err(got, want) < F32_TOL
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("spec", [moe(experts=6, top=2, ff=24), moe(experts=16, top=4, ff=8, shared_ff=0), moe(experts=3, top=3, ff=40, shared_ff=8),
+                                  moe(experts=70, top=5, ff=16)], ids=lambda s: "E%d-top%d" % (s["router"]["experts"], s["router"]["top"]))
+def test_sorted_experts_equal_stacked_experts(dev, monkeypatch, dtype, spec):
+    """The two ways to run the experts (sorted rows through grouped products; all experts stacked with zero weights for the unused) on the
+    same inputs, in a batch large enough that every expert gets rows and in one where most get none."""
+    from qserve_b200 import hybrid
+    from qserve_b200.modelcfg import MoeConfig
+
+    W, dt = 64, 1 if dtype == torch.float32 else 0
+    c = MoeConfig(spec["router"]["experts"], spec["router"]["top"], spec["expert"]["ff"], spec["expert"]["limit"],
+                  (spec.get("shared") or {}).get("ff", 0), (spec.get("shared") or {}).get("limit", 0.0))
+    cfg = make_config([gate_layer(mlp=spec)], width=W)
+    w = {k[len("l0.mlp."):]: v for k, v in make_weights(cfg, 14).items() if k.startswith("l0.mlp.")}
+    s = torch.cuda.current_stream().cuda_stream
+    ffs = {}
+    for impl in ("sorted", "dense"):
+        monkeypatch.setattr(hybrid, "MOE_IMPL", impl)
+        ffs[impl] = hybrid.MoeFeedForward(c, w, W, dtype, dev)
+        assert ffs[impl].impl == impl
+    for T in (300, 1, 3):
+        h = torch.randn(T, W, generator=torch.Generator().manual_seed(T)).to(dtype).to(dev)
+        a, a32 = ffs["sorted"].run(h, dt, s)
+        b, b32 = ffs["dense"].run(h, dt, s)
+        assert a32 and not b32
+        want = O.expert_mixture(h.double().cpu(), w, spec)
+        if dtype == torch.float32:
+            assert row_err(a, want) < 1e-5 and row_err(b, want) < 1e-5
+        else:  # the same router choices (same kernel, same input); the two differ by where they round
+            assert row_err(a, b) < 2e-2 and row_err(a, want) < 2e-2
+
+
 @pytest.mark.parametrize("streams,groups", [(0, 1), (1, 3), (4, 2)])
 def test_stack_of_layers(dev, streams, groups):
     cfg = make_config(MIXED, streams=streams, groups=groups)
@@ -150,8 +182,9 @@ def test_stack_of_layers(dev, streams, groups):
 
 
 # expert choices are left out of the bfloat16 comparisons (every expert runs): a close call of the router may fall the other way in 16 bits
-BF16 = [gate_layer(mlp=moe(experts=4, top=4)), pair_layer(mlp=moe(experts=4, top=4)), pair_layer(chunk=64, mlp=None),
-        gate_layer(heads=2, dim=64, vdim=16, mlp=moe(experts=2, top=2, shared_ff=0))]
+BF16 = [gate_layer(mlp=moe(experts=4, top=4)), pair_layer(mlp=moe(experts=4, top=4)),
+        pair_layer(heads=8, kv_heads=2, dim=32, vdim=64, chunk=50, r_heads=2, r_dim=64, r_vdim=32, rot_dims=32, mlp=None),  # the tensor-core kernels' sizes
+        gate_layer(heads=2, dim=64, vdim=16, mlp=moe(experts=2, top=2, ff=16, shared_ff=0))]
 
 
 def test_bfloat16_engine_stays_within_rounding(dev):
@@ -316,6 +349,64 @@ def test_one_key_inside_or_outside_the_chunk(dev, chunk, needle, seen, decode):
         eng.step([("a", toks[:130], [])])
         got = eng.step([("a", toks[130:], [n - 131])])
     assert row_err(got, want) < F32_TOL
+
+
+@pytest.mark.parametrize("chunk,needle,seen", [(0, 0, True), (100, 200, True), (100, 199, False), (64, 256, True), (64, 255, False), (300, 0, True),
+                                                (150, 150, True), (150, 149, False)])
+@pytest.mark.parametrize("decode", [False, True])
+def test_one_key_inside_or_outside_the_chunk_on_the_fast_kernels(dev, chunk, needle, seen, decode):
+    """The same in bfloat16 with head sizes the tensor-core prompt and single-token kernels take."""
+    n = 300
+    cfg, w, toks = _needle_model(n, needle, chunk, dim=16, vdim=32)
+    want = O.forward(cfg, w, toks)[-1:]
+    eng = _engine(cfg, w, torch.bfloat16)
+    if decode:
+        eng.step([("a", toks[:-1], [])])
+        got = eng.step([("a", toks[-1:], [0])])
+    else:
+        eng.step([("a", toks[:130], [])])
+        got = eng.step([("a", toks[130:], [n - 131])])
+    assert row_err(got, want) < 0.05
+
+
+@pytest.mark.parametrize("shape", [(4, 2, 16, 32, 24, 0, True), (6, 3, 48, 96, 100, 0, True), (8, 2, 32, 64, 64, 0, False), (2, 1, 64, 128, 1, 0, True),
+                                   (3, 3, 16, 256, 0, 37, True), (16, 1, 16, 32, 130, 50, True), (4, 4, 128, 128, 0, 0, True)],
+                         ids=lambda s: "H%d-G%d-D%d-Dv%d-chunk%d-window%d-sink%d" % s)
+def test_fast_attention_kernels_match_the_plain_kernel_with_masks_and_sinks(dev, shape):
+    """Same bfloat16 inputs and cache through the tensor-core kernels and through the plain kernel, with chunks, windows and sinks: prompt
+    portions with and without context, portions that cross chunk edges and end inside a page, short portions and single tokens in one batch."""
+    from qserve_b200.hybrid import MultiMapAttentionMixer, StepBatch
+    from qserve_b200.modelcfg import AttentionMixerConfig
+
+    H, G, D, Dv, chunk, window, sink = shape
+    m = AttentionMixerConfig(H, G, D, Dv, None, 2.0 * D ** -0.5, bias=True, qk_norm=True, head_temp=True, sink=sink, chunk=chunk, window=window)
+    g = torch.Generator().manual_seed(5)
+    r = lambda *s: torch.randn(*s, generator=g)
+    w = {"q": r(H * D, 8), "k": r(G * D, 8), "v": r(G * Dv, 8), "o": r(8, H * Dv), "q.b": r(H * D), "k.b": r(G * D), "v.b": r(G * Dv),
+         "temp": 1.0 + torch.rand(H, generator=g), "sink": r(H) + 2.0}
+    mixer = MultiMapAttentionMixer(m, w, 1e-5, torch.bfloat16, dev)
+    pages, page = 40, 64
+    kpool = torch.zeros(pages, page, G, D, dtype=torch.bfloat16, device=dev)
+    vpool = torch.zeros(pages, page, G, Dv, dtype=torch.bfloat16, device=dev)
+    table = torch.randperm(pages, generator=g).to(torch.int32).view(4, 10).to(dev)
+    steps = [[(0, 0, -1, [0] * 200), (1, 0, -1, [0] * 70), (2, 0, -1, [0] * 3), (3, 0, -1, [0] * 16)],
+             [(0, 200, 0, [0] * 1), (1, 70, 0, [0] * 130), (2, 3, 0, [0] * 15), (3, 16, 0, [0] * 64)],
+             [(0, 201, 0, [0] * 90), (1, 200, 0, [0] * 1), (2, 18, 0, [0] * 1), (3, 80, 0, [0] * 17)],
+             [(0, 291, 0, [0] * 15), (1, 201, 0, [0] * 15), (2, 19, 0, [0] * 15), (3, 97, 0, [0] * 15)],
+             [(0, 306, 0, [0] * 1), (3, 112, 0, [0] * 1)]]
+    for entries in steps:
+        b = StepBatch.build(entries, table, dev)
+        T = b.n_tokens
+        proj = (r(T, mixer.in_features) * 1.5).to(torch.bfloat16).to(dev)
+        outs = []
+        for fast in (True, False):
+            p2, out = proj.clone(), torch.zeros(T, H * Dv, dtype=torch.bfloat16, device=dev)
+            scratch = torch.empty(mixer.scratch_floats(T), dtype=torch.float32, device=dev) if fast else None
+            mixer.run(p2, out, b, {"k": kpool, "v": vpool}, page, scratch, 0, torch.cuda.current_stream().cuda_stream)
+            outs.append(out.float())
+        torch.cuda.synchronize()
+        d = (outs[0] - outs[1]).abs()
+        assert float(d.max()) <= 2.0 ** -6 * float(outs[1].abs().max()) and float(d.mean()) < 1e-3 * float(outs[1].abs().mean())
 
 
 def test_sink_takes_its_share(dev):
