@@ -57,6 +57,9 @@ def parse():
     ap.add_argument("--kernel-reps", type=int, default=5)
     ap.add_argument("--hybrid", action="store_true", help="instead of the default workload: prefill and decode throughput of the Rizurax hybrid decoder "
                     "(random weights) at layer sizes of real models, beside the Llama-style W4A8KV4 runner at equal size; prints one JSON line")
+    ap.add_argument("--toderax", action="store_true", help="instead of the default workload: prefill and decode throughput of the Toderax decoder "
+                    "(hyper-connection streams, gate recurrence, chunked sink attention beside retention, mixture of experts; random weights) at "
+                    "layer sizes of real models, beside the Rizurax hybrid decoder at equal size; prints one JSON line")
     return ap.parse_args()
 
 
@@ -762,6 +765,178 @@ def hybrid_block(args):
 
 
 # ------------------------------------------------------------------------------------------------------------
+# --toderax: the Toderax decoder beside the closest existing model (the Rizurax hybrid decoder) at equal size
+# ------------------------------------------------------------------------------------------------------------
+def toderax_block(args):
+    """Prefill (4 prompts x 2048 tokens in one step) and decode (64 sequences at 1024 tokens of context) of a four-layer stack
+    gate recurrence | attention + retention | gate recurrence | attention + retention with a mixture of experts (16 experts, 4 per token, plus a
+    shared expert; the experts a token runs hold as many weights as the other model's feed-forward) in every layer, on 4 residual streams.
+    Whole steps are captured in CUDA graphs (device time, host excluded); the design's kernels are timed one by one with their algorithmic
+    bytes / flops against the measured copy and bf16 GEMM peaks.  Beside it: the Rizurax stack (attention | delta | attention | delta, dense
+    feed-forward) at equal width / heads / head size, and the kernels that play the same parts there."""
+    import torch
+
+    from qserve_b200._lib import check, lib
+    from qserve_b200.engine import Engine
+    from qserve_b200.hybrid import HybridDecoder, StepBatch, random_weights
+    from qserve_b200.modelcfg import (AttentionMixerConfig, DeltaMixerConfig, GateRecurrenceMixerConfig, HybridConfig, HybridLayerConfig, MlpConfig,
+                                      MoeConfig, ParallelMixerConfig, RetentionMixerConfig, RotaryConfig)
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    hbm_gbs = peaks()[0]
+    try:
+        tflops = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["bf16_tflops"]
+    except (OSError, KeyError, ValueError):
+        tflops = 1590.0
+    stream = torch.cuda.current_stream()
+    reps = max(3, args.kernel_reps)
+    raw = lambda: torch._C._cuda_getCurrentRawStream(0)
+    B, CTX, NP, LP, NS, E, TOP = 64, 1024, 4, 2048, 4, 16, 4
+    out = {"metric": "Toderax decoder throughput (tokens/s, random weights, bf16, 4 layers)", "unit": "tokens/s", "impl": "ours", "dtype": "bf16",
+           "data": "synthetic", "peaks": {"hbm_gbs": hbm_gbs, "bf16_tflops": tflops}, "sizes": {}}
+
+    def steps(model, eng, V, g):
+        """Prefill and decode step times of a model; returns (record, prefill batch, decode batch)."""
+        prompts = [torch.randint(0, V, (LP,), generator=g).tolist() for _ in range(NP)]
+        for i, p_ in enumerate(prompts):
+            eng.cache.admit(("p", i)); eng.cache.reserve(("p", i), LP)
+        pb = StepBatch.build([(eng.cache.seqs[("p", i)].slot, 0, -1, p_) for i, p_ in enumerate(prompts)], eng.cache.sync_block_table(), dev)
+        t = time_kernel(lambda: (model.forward(pb, eng.cache), 1)[1], reps, stream)
+        rec = {"prefill": {"tokens": NP * LP, "ms": t * 1e3, "tokens_per_s": NP * LP / t}}
+        for i in range(B):
+            eng.cache.admit(("d", i)); eng.cache.reserve(("d", i), CTX + 1)
+        db = StepBatch.build([(eng.cache.seqs[("d", i)].slot, CTX, 5, [int(torch.randint(0, V, (1,), generator=g))]) for i in range(B)],
+                             eng.cache.sync_block_table(), dev)
+        t = time_kernel(lambda: (model.logits(model.forward(db, eng.cache)), 1)[1], reps * 4, stream)
+        rec["decode"] = {"batch": B, "ctx": CTX, "ms": t * 1e3, "tokens_per_s": B / t}
+        return rec, pb, db
+
+    def mixer_times(mixer, run_cache, pb, db, T):
+        proj = torch.randn(T, mixer.in_features, device=dev).to(torch.bfloat16)
+        cat = torch.empty(T, mixer.out_features, dtype=torch.bfloat16, device=dev)
+        scratch = torch.empty(max(1, mixer.scratch_floats(T)), dtype=torch.float32, device=dev)
+        tp = time_kernel(lambda: (mixer.run(proj, cat, pb, run_cache, 64, scratch, 0, raw()), 1)[1], reps, stream)
+        td = time_kernel(lambda: (mixer.run(proj[:B], cat[:B], db, run_cache, 64, scratch, 0, raw()), 1)[1], reps * 4, stream)
+        return tp, td
+
+    for name, (W, H, G, D, FF, V) in HYBRID_SIZES.items():
+        T = NP * LP
+        chunk = LP  # a prompt is one chunk and a decoded token sees its whole context: the same score work as the other model's causal attention
+        att = AttentionMixerConfig(H, G, D, D, None, D ** -0.5, bias=True, qk_norm=True, head_temp=True, sink=True, chunk=chunk)
+        ret = RetentionMixerConfig(H // 2, D, D, RotaryConfig(D, 1e6, layout="half"), tuple(1.0 - 2.0 ** (-5 - 5 * i / (H // 2)) for i in range(H // 2)))
+        par = ParallelMixerConfig(att, ret)
+        gate = GateRecurrenceMixerConfig(H, D, D)
+        moe = MoeConfig(E, TOP, FF // TOP, 7.0, FF // TOP, 7.0)
+        cfg = HybridConfig("Toderax", V, W, 1e-5, tuple(HybridLayerConfig(t, m, moe) for t, m in
+                                                       (("hgrn2", gate), ("parallel", par), ("hgrn2", gate), ("parallel", par))),
+                           norm_offset=0.0, block="sequential", streams=NS, norm_groups=4, embed_scale=4.0)
+        g = torch.Generator().manual_seed(0)
+        rec = {}
+        with torch.no_grad():
+            model = HybridDecoder(cfg, random_weights(cfg, 0, dev), torch.bfloat16, dev)
+            eng = Engine(model, max_tokens=B * (CTX + 64) + NP * LP, max_seqs=B + NP)
+            rec, pb, db = steps(model, eng, V, g)
+            kern = {}
+            ly_g, ly_p = model.layers[0], model.layers[1]
+            tp, td = mixer_times(ly_p.mixer.left, eng.cache.runs[1]["left"], pb, db, T)
+            flops = H * NP * (LP * (LP + 1) // 2) * 4 * D
+            kern["attention_prefill(prepare+append+attention)"] = {"us": tp * 1e6, "tflops": flops / tp / 1e12, "frac_of_measured_bf16_peak": flops / tp / 1e12 / tflops}
+            kern["attention_decode(prepare+append+attention)"] = {"us": td * 1e6, "frac_of_measured_hbm": B * (CTX + 1) * G * 2 * D * 2 / td / 1e9 / hbm_gbs}
+            tp, td = mixer_times(ly_g.mixer, eng.cache.runs[0], pb, db, T)
+            kern["gate_recurrence_prefill(prepare+scan+norm)"] = {"us": tp * 1e6, "tokens_per_s": T / tp, "heads": H}
+            kern["gate_recurrence_decode(prepare+scan+norm)"] = {"us": td * 1e6, "frac_of_measured_hbm": B * H * D * D * 8 / td / 1e9 / hbm_gbs}
+            tp, td = mixer_times(ly_p.mixer.right, eng.cache.runs[1]["right"], pb, db, T)
+            kern["retention_prefill(rotate+scan+gate)"] = {"us": tp * 1e6, "tokens_per_s": T / tp, "heads": H // 2}
+            kern["retention_decode(rotate+scan+gate)"] = {"us": td * 1e6, "frac_of_measured_hbm": B * (H // 2) * D * D * 8 / td / 1e9 / hbm_gbs}
+            # the streams' kernel as the engine runs it: a pending bf16 write lands in 4 fp32 streams, one normalised bf16 row leaves
+            x = torch.randn(T, NS, W, device=dev)
+            h1, upd = torch.empty(T, W, dtype=torch.bfloat16, device=dev), torch.zeros(T, W, dtype=torch.bfloat16, device=dev)
+            hc = ly_g.hc2
+            tn = time_kernel(lambda: (check(lib.qs_hyb_stream_norm(h1.data_ptr(), None, x.data_ptr(), NS, upd.data_ptr(), 0, hc.mix.data_ptr(),
+                                                                   hc.cout.data_ptr(), hc.cin.data_ptr(), ly_g.norm2.data_ptr(), 4, 0.0, 1e-5, T, W, 0,
+                                                                   raw())), 1)[1], reps, stream)
+            kern["stream_write_read_group_norm(4 streams)"] = {"us": tn * 1e6, "frac_of_measured_hbm": T * W * (NS * 8 + 4) / tn / 1e9 / hbm_gbs}
+            ya, yb, y32 = torch.randn(T, W, device=dev).bfloat16(), torch.randn(T, W, device=dev).bfloat16(), torch.empty(T, W, device=dev)
+            tb = time_kernel(lambda: (check(lib.qs_hyb_branch_norm_mean(y32.data_ptr(), ya.data_ptr(), yb.data_ptr(), ly_p.mixer.gain_left.data_ptr(),
+                                                                        ly_p.mixer.gain_right.data_ptr(), 0.5, 1e-5, T, W, 0, raw())), 1)[1], reps, stream)
+            kern["branch_norm_mean"] = {"us": tb * 1e6, "frac_of_measured_hbm": T * W * 8 / tb / 1e9 / hbm_gbs}
+            del x, upd, ya, yb, y32
+            # the feed-forward: useful flops are those of the experts a token runs and the shared expert
+            h = torch.randn(T, W, device=dev).to(torch.bfloat16)
+            ffl = 2 * 3 * W * (TOP * moe.ff + moe.shared_ff)
+            for label, hh, r_ in (("prefill", h, reps), ("decode", h[:B].contiguous(), reps * 4)):
+                tm = time_kernel(lambda: (ly_g.ff.run(hh, 0, raw()), 1)[1], r_, stream)
+                n = hh.shape[0]
+                kern[f"moe_feed_forward_{label}(router+sort+gather+4 products+act+combine)"] = {
+                    "us": tm * 1e6, "tflops": n * ffl / tm / 1e12, "frac_of_measured_bf16_peak": n * ffl / tm / 1e12 / tflops,
+                    "weights_frac_of_measured_hbm": 3 * W * (min(E, n * TOP) * moe.ff + moe.shared_ff) * 2 / tm / 1e9 / hbm_gbs}
+            route, ti, tw = torch.empty(T, E, device=dev), torch.empty(T, TOP, dtype=torch.int32, device=dev), torch.empty(T, TOP, device=dev)
+            tr = time_kernel(lambda: (check(lib.qs_hyb_moe_router(route.data_ptr(), ti.data_ptr(), tw.data_ptr(), h.data_ptr(), ly_g.ff.w_router.data_ptr(),
+                                                                  T, W, E, TOP, 0, raw())), 1)[1], reps, stream)
+            kern["moe_router"] = {"us": tr * 1e6, "frac_of_measured_hbm": T * W * 2 / tr / 1e9 / hbm_gbs}
+            gu = torch.randn(T * TOP, 2 * moe.ff, device=dev).to(torch.bfloat16)
+            act = torch.empty(T * TOP, moe.ff, dtype=torch.bfloat16, device=dev)
+            ta = time_kernel(lambda: (check(lib.qs_hyb_moe_act(act.data_ptr(), gu.data_ptr(), None, T * TOP, 0, 0, 0.0, moe.ff, 7.0, 1.702, 0, raw())), 1)[1],
+                             reps, stream)
+            kern["moe_clamped_activation"] = {"us": ta * 1e6, "frac_of_measured_hbm": T * TOP * moe.ff * 6 / ta / 1e9 / hbm_gbs}
+            rec["kernels"] = kern
+            del eng, model, h, gu, act
+        torch.cuda.empty_cache()
+        # ---- the closest existing model at equal size: Rizurax (differential attention | gated delta rule, dense feed-forward)
+        ratt = AttentionMixerConfig(H, G, D, D, RotaryConfig(D // 2, 1e6, 4.0, 4096, 32.0, 1.0), D ** -0.5, maps=2, diff=0.5, head_norm=True)
+        rdlt = DeltaMixerConfig(H, G, D, D, 4)
+        rcfg = HybridConfig("Rizurax", V, W, 1e-5, tuple(HybridLayerConfig(t, m, MlpConfig("dense", FF)) for t, m in
+                                                        (("attention", ratt), ("delta", rdlt), ("attention", ratt), ("delta", rdlt))),
+                            pair_buckets=4093, pair_mul_prev=131, pair_mul_cur=11)
+        with torch.no_grad():
+            model = HybridDecoder(rcfg, random_weights(rcfg, 0, dev), torch.bfloat16, dev)
+            eng = Engine(model, max_tokens=B * (CTX + 64) + NP * LP, max_seqs=B + NP)
+            peer, pb, db = steps(model, eng, V, g)
+            kern = {}
+            tp, td = mixer_times(model.layers[0].mixer, eng.cache.runs[0], pb, db, T)
+            flops = H * NP * (LP * (LP + 1) // 2) * 8 * D
+            kern["attention_prefill(rope+append+attention, 2 maps)"] = {"us": tp * 1e6, "tflops": flops / tp / 1e12, "frac_of_measured_bf16_peak": flops / tp / 1e12 / tflops}
+            kern["attention_decode(rope+append+attention, 2 maps)"] = {"us": td * 1e6, "frac_of_measured_hbm": B * (CTX + 1) * G * 3 * D * 2 / td / 1e9 / hbm_gbs}
+            tp, td = mixer_times(model.layers[1].mixer, eng.cache.runs[1], pb, db, T)
+            kern["delta_prefill(conv+scan+gate)"] = {"us": tp * 1e6, "tokens_per_s": T / tp, "heads": H}
+            kern["delta_decode(conv+scan+gate)"] = {"us": td * 1e6, "frac_of_measured_hbm": B * H * D * D * 8 / td / 1e9 / hbm_gbs}
+            ly = model.layers[0]
+            x = torch.randn(T, W, device=dev)
+            h1, h2 = torch.empty(T, W, dtype=torch.bfloat16, device=dev), torch.empty(T, W, dtype=torch.bfloat16, device=dev)
+            upd = torch.zeros(T, W, dtype=torch.bfloat16, device=dev)
+            tn = time_kernel(lambda: (check(lib.qs_hyb_rms_norm(h1.data_ptr(), h2.data_ptr(), x.data_ptr(), upd.data_ptr(), ly.norm1.data_ptr(),
+                                                                 ly.norm2.data_ptr(), 1.0, 1e-5, T, W, 0, raw())), 1)[1], reps, stream)
+            kern["add_rms_norm_dual"] = {"us": tn * 1e6, "frac_of_measured_hbm": T * W * 14 / tn / 1e9 / hbm_gbs}
+            del x, upd
+            # its feed-forward as the engine runs it: gate | up product, gelu-tanh gate, down product (here without the attention half of the row)
+            w_dn = torch.randn(W, FF, device=dev).to(torch.bfloat16)
+            for label, hh, r_ in (("prefill", h1, reps), ("decode", h1[:B].contiguous(), reps * 4)):
+                n = hh.shape[0]
+                cat = torch.empty(n, FF, dtype=torch.bfloat16, device=dev)
+
+                def ffn():
+                    gu_ = torch.mm(hh, ly.w_mlp_in.t())
+                    check(lib.qs_hyb_gelu_tanh_mul(cat.data_ptr(), cat.stride(0), gu_.data_ptr(), n, FF, 0, raw()))
+                    torch.mm(cat, w_dn.t())
+                    return 1
+                tm = time_kernel(ffn, r_, stream)
+                kern[f"dense_feed_forward_{label}(2 products+act)"] = {"us": tm * 1e6, "tflops": n * 6 * W * FF / tm / 1e12,
+                                                                      "frac_of_measured_bf16_peak": n * 6 * W * FF / tm / 1e12 / tflops,
+                                                                      "weights_frac_of_measured_hbm": 3 * W * FF * 2 / tm / 1e9 / hbm_gbs}
+            gu = torch.randn(T, 2 * FF, device=dev).to(torch.bfloat16)
+            cat = torch.empty(T, FF, dtype=torch.bfloat16, device=dev)
+            tg = time_kernel(lambda: (check(lib.qs_hyb_gelu_tanh_mul(cat.data_ptr(), cat.stride(0), gu.data_ptr(), T, FF, 0, raw())), 1)[1], reps, stream)
+            kern["gelu_tanh_mul"] = {"us": tg * 1e6, "frac_of_measured_hbm": T * FF * 6 / tg / 1e9 / hbm_gbs}
+            peer["kernels"] = kern
+            del eng, model, gu, cat, h1, h2, w_dn
+        torch.cuda.empty_cache()
+        rec["rizurax_equal_size"] = peer
+        out["sizes"][name] = rec
+    print(json.dumps(out), flush=True)
+
+
+# ------------------------------------------------------------------------------------------------------------
 def main():
     args = parse()
     rank = int(os.environ.get("RANK", "0"))
@@ -773,6 +948,10 @@ def main():
     if args.hybrid:
         if rank == 0:
             hybrid_block(args)
+        return
+    if args.toderax:
+        if rank == 0:
+            toderax_block(args)
         return
     if args.impl == "reference-gpu":
         if rank == 0:

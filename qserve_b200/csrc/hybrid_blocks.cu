@@ -100,6 +100,85 @@ __global__ void stream_norm_kernel(ST* __restrict__ out_h, float* __restrict__ o
   for (int i = tid; i < W; i += blockDim.x) stf(out_h + (size_t)t * W + i, u_s[i] * rinv[i / part] * (offset + w[i]));
 }
 
+// the same for widths that are multiples of 4 and 16-byte aligned rows: four columns per thread, the stream count a compile-time constant
+template <typename ST, int S>
+__global__ void stream_norm_vec_kernel(ST* __restrict__ out_h, float* __restrict__ out_sum, float* __restrict__ x, const void* __restrict__ upd,
+                                       int upd_f32, const float* __restrict__ mix, const float* __restrict__ cout, const float* __restrict__ cin,
+                                       const float* __restrict__ w, int groups, float offset, float eps, int W) {
+  extern __shared__ __align__(16) float dyn[];  // u [W] | partial sums [groups * per] | 1 / rms [groups]
+  __shared__ float c_mix[S * S], c_out[S], c_in[S];
+  const int t = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nw = blockDim.x >> 5;
+  if (tid < S * S) c_mix[tid] = upd != nullptr ? mix[tid] : 0.f;
+  if (tid < S) {
+    c_out[tid] = upd != nullptr ? cout[tid] : 0.f;
+    c_in[tid] = cin != nullptr ? cin[tid] : 1.f;
+  }
+  __syncthreads();
+  float* u_s = dyn;
+  float* xr = x + (size_t)t * S * W;
+  for (int i = tid * 4; i < W; i += blockDim.x * 4) {
+    float4 xs[S];
+#pragma unroll
+    for (int s = 0; s < S; ++s) xs[s] = ld4(xr + (size_t)s * W + i);
+    if (upd != nullptr) {
+      const float4 y = upd_f32 ? ld4(static_cast<const float*>(upd) + (size_t)t * W + i) : ld4(static_cast<const ST*>(upd) + (size_t)t * W + i);
+      float4 nx[S];
+#pragma unroll
+      for (int d = 0; d < S; ++d) {
+        float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int s = 0; s < S; ++s) {
+          const float m = c_mix[s * S + d];
+          a.x += m * xs[s].x; a.y += m * xs[s].y; a.z += m * xs[s].z; a.w += m * xs[s].w;
+        }
+        const float o = c_out[d];
+        nx[d] = make_float4(a.x + o * y.x, a.y + o * y.y, a.z + o * y.z, a.w + o * y.w);
+      }
+#pragma unroll
+      for (int d = 0; d < S; ++d) {
+        xs[d] = nx[d];
+        st4(xr + (size_t)d * W + i, nx[d]);
+      }
+    }
+    float4 u = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int s = 0; s < S; ++s) {
+      const float c = c_in[s];
+      u.x += c * xs[s].x; u.y += c * xs[s].y; u.z += c * xs[s].z; u.w += c * xs[s].w;
+    }
+    *reinterpret_cast<float4*>(u_s + i) = u;
+    if (out_sum != nullptr) st4(out_sum + (size_t)t * W + i, u);
+  }
+  if (out_h == nullptr) return;
+  __syncthreads();
+  const int part = W / groups, per = max(1, nw / groups), units = groups * per, len = (part + per - 1) / per;
+  float* partial = dyn + W;
+  float* rinv = partial + units;
+  for (int un = warp; un < units; un += nw) {
+    const int g = un / per, sub = un - g * per;
+    const int lo = sub * len, hi = min(part, lo + len);
+    float ss = 0.f;
+    for (int i = lo + lane; i < hi; i += 32) {
+      const float v = u_s[g * part + i];
+      ss += v * v;
+    }
+    ss = warp_sum(ss);
+    if (lane == 0) partial[un] = ss;
+  }
+  __syncthreads();
+  for (int g = tid; g < groups; g += blockDim.x) {
+    float ss = 0.f;
+    for (int sub = 0; sub < per; ++sub) ss += partial[g * per + sub];
+    rinv[g] = 1.f / sqrtf(ss / (float)part + eps);
+  }
+  __syncthreads();
+  for (int i = tid * 4; i < W; i += blockDim.x * 4) {
+    const float4 u = *reinterpret_cast<const float4*>(u_s + i), g = ld4(w + i);
+    st4(out_h + (size_t)t * W + i, make_float4(u.x * rinv[i / part] * (offset + g.x), u.y * rinv[(i + 1) / part] * (offset + g.y),
+                                               u.z * rinv[(i + 2) / part] * (offset + g.z), u.w * rinv[(i + 3) / part] * (offset + g.w)));
+  }
+}
+
 // y = scale * (a * rsqrt(mean(a^2) + eps) * wa + b * rsqrt(mean(b^2) + eps) * wb): two branches, each normed over the whole row with its own
 // gain; y fp32
 template <typename ST>
@@ -117,6 +196,28 @@ __global__ void branch_norm_mean_kernel(float* __restrict__ y, const ST* __restr
   sb = block_sum(sb, red);
   const float ra = 1.f / sqrtf(sa / (float)W + eps), rb = 1.f / sqrtf(sb / (float)W + eps);
   for (int i = threadIdx.x; i < W; i += blockDim.x) y[base + i] = scale * (ldf(a + base + i) * ra * wa[i] + ldf(b + base + i) * rb * wb[i]);
+}
+
+// the same for widths that are multiples of 4 and 16-byte aligned rows
+template <typename ST>
+__global__ void branch_norm_mean_vec_kernel(float* __restrict__ y, const ST* __restrict__ a, const ST* __restrict__ b, const float* __restrict__ wa,
+                                            const float* __restrict__ wb, float scale, float eps, int W) {
+  __shared__ float red[33];
+  const size_t base = (size_t)blockIdx.x * W;
+  float sa = 0.f, sb = 0.f;
+  for (int i = threadIdx.x * 4; i < W; i += blockDim.x * 4) {
+    const float4 va = ld4(a + base + i), vb = ld4(b + base + i);
+    sa += va.x * va.x + va.y * va.y + va.z * va.z + va.w * va.w;
+    sb += vb.x * vb.x + vb.y * vb.y + vb.z * vb.z + vb.w * vb.w;
+  }
+  sa = block_sum(sa, red);
+  sb = block_sum(sb, red);
+  const float ra = scale / sqrtf(sa / (float)W + eps), rb = scale / sqrtf(sb / (float)W + eps);
+  for (int i = threadIdx.x * 4; i < W; i += blockDim.x * 4) {
+    const float4 va = ld4(a + base + i), vb = ld4(b + base + i), ga = ld4(wa + i), gb = ld4(wb + i);
+    st4(y + base + i, make_float4(va.x * ra * ga.x + vb.x * rb * gb.x, va.y * ra * ga.y + vb.y * rb * gb.y, va.z * ra * ga.z + vb.z * rb * gb.z,
+                                  va.w * ra * ga.w + vb.w * rb * gb.w));
+  }
 }
 
 // ---------------------------------------------------------------------------------------------------------------------------------
@@ -260,6 +361,39 @@ __global__ void moe_act_kernel(ST* __restrict__ out, const ST* __restrict__ in, 
   stf(out + (size_t)t * F + j, y);
 }
 
+// bfloat16 rows, eight columns per thread (expert sizes that are multiples of 8: a thread's columns belong to one expert).
+// sigmoid(alpha g) = 1 / (1 + 2^(-alpha g log2 e)): one exponential and one division on the special-function unit, far below the rounding of
+// the bfloat16 result
+__global__ void moe_act_bf16x8_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ in, const float* __restrict__ route, int E,
+                                      int ff, float limit, int ff_shared, float limit_shared, float alpha) {
+  const int t = blockIdx.x;
+  const int F = E * ff + ff_shared;
+  const int j = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
+  if (j >= F) return;
+  float wgt = 1.f, lim = limit_shared;
+  if (j < E * ff) {
+    wgt = route[(size_t)t * E + j / ff];
+    lim = limit;
+  }
+  __nv_bfloat16* o = out + (size_t)t * F + j;
+  if (wgt == 0.f) {
+    *reinterpret_cast<uint4*>(o) = make_uint4(0, 0, 0, 0);
+    return;
+  }
+  const __nv_bfloat16* row = in + (size_t)t * 2 * F;
+  const float4 g0 = ld4(row + j), g1 = ld4(row + j + 4), u0 = ld4(row + F + j), u1 = ld4(row + F + j + 4);
+  const float na = -alpha * 1.4426950408889634f;
+  auto f = [&](float g, float u) {
+    g = fminf(g, lim);
+    u = fminf(fmaxf(u, -lim), lim);
+    float e;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(na * g));
+    return wgt * __fdividef(g, 1.f + e) * (u + 1.f);
+  };
+  st4(o, make_float4(f(g0.x, u0.x), f(g0.y, u0.y), f(g0.z, u0.z), f(g0.w, u0.w)));
+  st4(o + 4, make_float4(f(g1.x, u1.x), f(g1.y, u1.y), f(g1.z, u1.z), f(g1.w, u1.w)));
+}
+
 // ---------------------------------------------------------------------------------------------------------------------------------
 // Expert-sorted rows.  Entry i = token * top + choice of top_idx names an expert; the entries of expert 0 come first, then expert 1's, ...,
 // each expert's in token order (so the order never depends on timing).  Two kernels, one block per expert:
@@ -376,6 +510,30 @@ int qs_hyb_stream_norm(void* out_h, float* out_sum, float* x, int streams, const
     stream_norm_kernel<ST><<<tokens_n, threads, smb, s>>>((ST*)out_h, out_sum, x, streams, upd, upd_f32, upd_mix, upd_out, in_coef, w,  \
                                                          groups, offset, eps, width);                                                  \
   } while (0)
+  auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+  if (width % 4 == 0 && al16(out_h) && al16(out_sum) && al16(x) && al16(upd) && al16(w)) {
+#define QS_VEC(ST, S)                                                                                                                        \
+  do {                                                                                                                                       \
+    if (smb > 48 * 1024) cudaFuncSetAttribute(stream_norm_vec_kernel<ST, S>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smb);         \
+    stream_norm_vec_kernel<ST, S><<<tokens_n, threads, smb, s>>>((ST*)out_h, out_sum, x, upd, upd_f32, upd_mix, upd_out, in_coef, w, groups,  \
+                                                                offset, eps, width);                                                        \
+  } while (0)
+#define QS_VEC_S(ST)                        \
+  switch (streams) {                        \
+    case 1: QS_VEC(ST, 1); break;           \
+    case 2: QS_VEC(ST, 2); break;           \
+    case 3: QS_VEC(ST, 3); break;           \
+    case 4: QS_VEC(ST, 4); break;           \
+    case 5: QS_VEC(ST, 5); break;           \
+    case 6: QS_VEC(ST, 6); break;           \
+    case 7: QS_VEC(ST, 7); break;           \
+    default: QS_VEC(ST, 8); break;          \
+  }
+    QS_DT(dtype, QS_VEC_S(__nv_bfloat16), QS_VEC_S(float));
+#undef QS_VEC_S
+#undef QS_VEC
+    return check_cuda(cudaGetLastError(), "hyb_stream_norm");
+  }
   QS_DT(dtype, QS_LAUNCH(__nv_bfloat16), QS_LAUNCH(float));
 #undef QS_LAUNCH
   return check_cuda(cudaGetLastError(), "hyb_stream_norm");
@@ -387,6 +545,13 @@ int qs_hyb_branch_norm_mean(float* y, const void* a, const void* b, const float*
   if (tokens_n == 0) return qs::QS_OK;
   cudaStream_t s = (cudaStream_t)stream;
   const int threads = width >= 1024 ? 256 : 128;
+  auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+  if (width % 4 == 0 && al16(y) && al16(a) && al16(b) && al16(wa) && al16(wb)) {
+    QS_DT(dtype,
+          (branch_norm_mean_vec_kernel<__nv_bfloat16><<<tokens_n, threads, 0, s>>>(y, (const __nv_bfloat16*)a, (const __nv_bfloat16*)b, wa, wb, scale, eps, width)),
+          (branch_norm_mean_vec_kernel<float><<<tokens_n, threads, 0, s>>>(y, (const float*)a, (const float*)b, wa, wb, scale, eps, width)));
+    return check_cuda(cudaGetLastError(), "hyb_branch_norm_mean");
+  }
   QS_DT(dtype,
         (branch_norm_mean_kernel<__nv_bfloat16><<<tokens_n, threads, 0, s>>>(y, (const __nv_bfloat16*)a, (const __nv_bfloat16*)b, wa, wb, scale, eps, width)),
         (branch_norm_mean_kernel<float><<<tokens_n, threads, 0, s>>>(y, (const float*)a, (const float*)b, wa, wb, scale, eps, width)));
@@ -440,6 +605,12 @@ int qs_hyb_moe_act(void* out, const void* in, const float* route, int tokens_n, 
   if (tokens_n == 0) return qs::QS_OK;
   cudaStream_t s = (cudaStream_t)stream;
   const int F = experts * ff + ff_shared;
+  if (dtype == QS_DTYPE_BF16 && ff % 8 == 0 && ff_shared % 8 == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0 &&
+      (reinterpret_cast<uintptr_t>(in) & 15) == 0) {
+    moe_act_bf16x8_kernel<<<dim3(tokens_n, (F / 8 + 255) / 256), 256, 0, s>>>((__nv_bfloat16*)out, (const __nv_bfloat16*)in, route, experts, ff, limit,
+                                                                              ff_shared, limit_shared, alpha);
+    return check_cuda(cudaGetLastError(), "hyb_moe_act");
+  }
   dim3 grid(tokens_n, (F + 255) / 256);
   QS_DT(dtype,
         (moe_act_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((__nv_bfloat16*)out, (const __nv_bfloat16*)in, route, experts, ff, limit, ff_shared,

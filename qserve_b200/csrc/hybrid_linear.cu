@@ -53,9 +53,12 @@ __global__ void gate_prepare_kernel(float* __restrict__ prep, const ST* __restri
 template <typename ST>
 __global__ void retention_prepare_kernel(float* __restrict__ prep, const ST* __restrict__ proj, long long stride, const int* __restrict__ tok_pos,
                                          const float* __restrict__ inv_freq, int rot_dims, float k_scale, int H, int D, int Dv) {
+  extern __shared__ float cs[];  // cos [rot_dims / 2] | sin [rot_dims / 2] of the token's position: one evaluation serves q and k of every head
   const int t = blockIdx.x;
   const int HD = H * D, half = rot_dims >> 1;
   const float pos = (float)tok_pos[t];
+  for (int p = threadIdx.x; p < half; p += blockDim.x) sincosf(pos * inv_freq[p], &cs[half + p], &cs[p]);
+  __syncthreads();
   const ST* row = proj + (size_t)t * stride;
   float* o = prep + (size_t)t * (2 * HD + H * Dv);
   for (int c = threadIdx.x; c < 2 * HD + H * Dv; c += blockDim.x) {
@@ -65,9 +68,8 @@ __global__ void retention_prepare_kernel(float* __restrict__ prep, const ST* __r
       if (d < rot_dims) {
         const bool first = d < half;
         const float other = ldf(row + (first ? c + half : c - half));
-        float sn, cs;
-        sincosf(pos * inv_freq[first ? d : d - half], &sn, &cs);
-        y = first ? y * cs - other * sn : y * cs + other * sn;
+        const int p = first ? d : d - half;
+        y = first ? y * cs[p] - other * cs[half + p] : y * cs[p] + other * cs[half + p];
       }
       if (c >= HD) y *= k_scale;
     }
@@ -290,9 +292,9 @@ int qs_hyb_retention(void* out, int64_t out_stride, float* prep, float* o_raw, c
   if (tokens_n == 0) return qs::QS_OK;
   cudaStream_t s = (cudaStream_t)stream;
   QS_DT(dtype,
-        (retention_prepare_kernel<__nv_bfloat16><<<tokens_n, 256, 0, s>>>(prep, (const __nv_bfloat16*)proj, stride, tok_pos, inv_freq, rot_dims, k_scale,
+        (retention_prepare_kernel<__nv_bfloat16><<<tokens_n, 256, rot_dims * sizeof(float), s>>>(prep, (const __nv_bfloat16*)proj, stride, tok_pos, inv_freq, rot_dims, k_scale,
                                                                            heads, dim, vdim)),
-        (retention_prepare_kernel<float><<<tokens_n, 256, 0, s>>>(prep, (const float*)proj, stride, tok_pos, inv_freq, rot_dims, k_scale, heads, dim,
+        (retention_prepare_kernel<float><<<tokens_n, 256, rot_dims * sizeof(float), s>>>(prep, (const float*)proj, stride, tok_pos, inv_freq, rot_dims, k_scale, heads, dim,
                                                                   vdim)));
   if (int rc = launch_scan<false>(o_raw, prep, state, head_decay, entry_start, entry_len, entry_slot, entry_pos0, entries, heads, dim, vdim, s)) return rc;
   const int warps = tokens_n * heads;

@@ -638,25 +638,65 @@ def random_weights(cfg: HybridConfig, seed: int = 0, device: Optional[torch.devi
     def r(*shape, s=1.0):
         return (torch.randn(*shape, generator=g, device=device) * s).to(dtype)
 
-    w = {"embed": r(cfg.vocab, W), "head": r(cfg.vocab, W, s=W ** -0.5), "final.norm": r(W, s=0.1)}
+    def mixer_weights(p: str, m) -> None:
+        if isinstance(m, ParallelMixerConfig):
+            mixer_weights(p + "left.", m.left)
+            mixer_weights(p + "right.", m.right)
+            w[p + "left.out"], w[p + "right.out"] = 1.0 + r(W, s=0.1), 1.0 + r(W, s=0.1)
+            return
+        H, D, Dv = m.heads, m.dim, m.vdim
+        if isinstance(m, AttentionMixerConfig):
+            G = m.kv_heads
+            w[p + "q"], w[p + "k"], w[p + "v"] = r(H * m.maps * D, W, s=W ** -0.5), r(G * m.maps * D, W, s=W ** -0.5), r(G * Dv, W, s=W ** -0.5)
+            if m.maps == 2:
+                for n in ("lq1", "lk1", "lq2", "lk2"):
+                    w[p + n] = r(D, s=0.1)
+            if m.bias:
+                w[p + "q.b"], w[p + "k.b"], w[p + "v.b"] = r(H * D, s=0.1), r(G * D, s=0.1), r(G * Dv, s=0.1)
+            if m.head_temp:
+                w[p + "temp"] = 1.0 + r(H, s=0.1)
+            if m.sink:
+                w[p + "sink"] = r(H, s=0.5)
+        elif isinstance(m, DeltaMixerConfig):
+            G = m.kv_heads
+            w[p + "q"], w[p + "k"], w[p + "v"] = r(G * D, W, s=W ** -0.5), r(G * D, W, s=W ** -0.5), r(H * Dv, W, s=W ** -0.5)
+            for n, c in (("q", G * D), ("k", G * D), ("v", H * Dv)):
+                w[p + f"{n}.conv"] = r(c, m.conv, s=0.5)
+            w[p + "b"], w[p + "a"], w[p + "g"] = r(H, W, s=W ** -0.5), r(H, W, s=W ** -0.5), r(H * Dv, W, s=W ** -0.5)
+            w[p + "A_log"], w[p + "dt_bias"], w[p + "norm"] = r(H, s=0.5), r(H, s=0.5), 1.0 + r(Dv, s=0.1)
+        elif isinstance(m, GateRecurrenceMixerConfig):
+            w[p + "q"], w[p + "f"], w[p + "v"] = r(H * D, W, s=W ** -0.5), r(H * D, W, s=W ** -0.5), r(H * Dv, W, s=W ** -0.5)
+            w[p + "f.b"], w[p + "lower"], w[p + "norm"] = r(H * D, s=0.5), torch.sigmoid(r(H * D).float()).to(dtype), 1.0 + r(Dv, s=0.1)
+        elif isinstance(m, RetentionMixerConfig):
+            w[p + "q"], w[p + "k"], w[p + "v"] = r(H * D, W, s=W ** -0.5), r(H * D, W, s=W ** -0.5), r(H * Dv, W, s=W ** -0.5)
+            if m.gated:
+                w[p + "g"] = r(H * Dv, W, s=W ** -0.5)
+        else:
+            raise TypeError(type(m))
+        w[p + "o"] = r(W, H * Dv, s=(H * Dv) ** -0.5)
+
+    gain = (lambda: 1.0 + r(W, s=0.1)) if cfg.norm_offset == 0.0 else (lambda: r(W, s=0.1))
+    w = {"embed": r(cfg.vocab, W), "head": r(cfg.vocab, W, s=W ** -0.5), "final.norm": gain()}
     if cfg.pair_buckets:
         w["bigram"] = r(cfg.pair_buckets + 1, W, s=0.5)
     for i, ly in enumerate(cfg.layers):
-        p, m = f"l{i}.", ly.mixer
-        H, G, D, Dv = m.heads, m.kv_heads, m.dim, m.vdim
-        w[p + "norm1"] = r(W, s=0.1)
-        if isinstance(m, AttentionMixerConfig):
-            w[p + "mix.q"], w[p + "mix.k"], w[p + "mix.v"] = r(H * m.maps * D, W, s=W ** -0.5), r(G * m.maps * D, W, s=W ** -0.5), r(G * Dv, W, s=W ** -0.5)
-            for n in ("lq1", "lk1", "lq2", "lk2"):
-                w[p + "mix." + n] = r(D, s=0.1)
-        else:
-            w[p + "mix.q"], w[p + "mix.k"], w[p + "mix.v"] = r(G * D, W, s=W ** -0.5), r(G * D, W, s=W ** -0.5), r(H * Dv, W, s=W ** -0.5)
-            for n, c in (("q", G * D), ("k", G * D), ("v", H * Dv)):
-                w[p + f"mix.{n}.conv"] = r(c, m.conv, s=0.5)
-            w[p + "mix.b"], w[p + "mix.a"], w[p + "mix.g"] = r(H, W, s=W ** -0.5), r(H, W, s=W ** -0.5), r(H * Dv, W, s=W ** -0.5)
-            w[p + "mix.A_log"], w[p + "mix.dt_bias"], w[p + "mix.norm"] = r(H, s=0.5), r(H, s=0.5), 1.0 + r(Dv, s=0.1)
-        w[p + "mix.o"] = r(W, H * Dv, s=(H * Dv) ** -0.5)
+        p = f"l{i}."
+        w[p + "norm1"] = gain()
+        mixer_weights(p + "mix.", ly.mixer)
         if ly.mlp is not None:
-            w[p + "norm2"] = r(W, s=0.1)
-            w[p + "mlp.gate"], w[p + "mlp.up"], w[p + "mlp.down"] = r(ly.mlp.ff, W, s=W ** -0.5), r(ly.mlp.ff, W, s=W ** -0.5), r(W, ly.mlp.ff, s=ly.mlp.ff ** -0.5)
+            w[p + "norm2"] = gain()
+            if isinstance(ly.mlp, MoeConfig):
+                c = ly.mlp
+                for n in [f"e{e}" for e in range(c.experts)] + (["shared"] if c.shared_ff else []):
+                    ff = c.shared_ff if n == "shared" else c.ff
+                    w[f"{p}mlp.{n}.gate"], w[f"{p}mlp.{n}.up"], w[f"{p}mlp.{n}.down"] = r(ff, W, s=W ** -0.5), r(ff, W, s=W ** -0.5), r(W, ff, s=ff ** -0.5)
+                w[p + "mlp.router"] = r(c.experts, W, s=W ** -0.5)
+            else:
+                w[p + "mlp.gate"], w[p + "mlp.up"], w[p + "mlp.down"] = r(ly.mlp.ff, W, s=W ** -0.5), r(ly.mlp.ff, W, s=W ** -0.5), r(W, ly.mlp.ff, s=ly.mlp.ff ** -0.5)
+        if cfg.streams > 0:
+            ns = cfg.streams
+            for q in (1, 2) if ly.mlp is not None else (1,):
+                w[f"{p}hc{q}.in"] = (torch.full((ns,), 1.0 / ns, device=device) + torch.randn(ns, generator=g, device=device) * 0.05).to(dtype)
+                w[f"{p}hc{q}.out"] = (1.0 + torch.randn(ns, generator=g, device=device) * 0.05).to(dtype)
+                w[f"{p}hc{q}.mix"] = (torch.eye(ns, device=device) + torch.randn(ns, ns, generator=g, device=device) * 0.02).to(dtype)
     return w
