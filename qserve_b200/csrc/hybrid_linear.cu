@@ -91,27 +91,29 @@ __device__ __forceinline__ float part_sum(float v) {
   return v;
 }
 
-template <int DP, int PARTS, int CH, bool CHANNEL_GATE, bool VEC>  // VEC: 16-byte staging (D, Dv, the prepared row and its base allow it)
+template <int DP, int PARTS, int CH, int CPT, bool CHANNEL_GATE, bool VEC>  // VEC: 16-byte staging (D, Dv, the prepared row and its base allow it)
 __global__ void __launch_bounds__(128) linear_scan_kernel(float* __restrict__ o_raw, const float* __restrict__ prep, float* __restrict__ state,
                                                           const float* __restrict__ head_decay, const int* __restrict__ entry_start,
                                                           const int* __restrict__ entry_len, const int* __restrict__ entry_slot,
                                                           const int* __restrict__ entry_pos0, int H, int D, int Dv) {
   extern __shared__ __align__(16) float sm[];  // [2][CH][ROW]
-  constexpr int Q = DP / PARTS, SEG = Q + 4, COLS = 128 / PARTS;  // a part's q / g segment is padded by 16 bytes: parts hit different banks
+  constexpr int Q = DP / PARTS, SEG = Q + 4, COLS = 128 / PARTS * CPT;  // a part's q / g segment is padded by 16 bytes: parts hit different banks
   constexpr int QK = PARTS * SEG, ROW = 2 * QK + COLS;
   const int e = blockIdx.x, h = blockIdx.y, cg = blockIdx.z;
-  const int tid = threadIdx.x, part = tid % PARTS, cl = tid / PARTS, col = cg * COLS + cl;
+  const int tid = threadIdx.x, part = tid % PARTS, cl = tid / PARTS, col0 = cg * COLS + cl * CPT;  // CPT adjacent columns per thread
   const int HD = H * D, P = 2 * HD + H * Dv;
   const int n = entry_len[e], s0 = entry_start[e];
   const bool fresh = entry_pos0[e] == 0;
   const float decay = CHANNEL_GATE ? 0.f : head_decay[h];
   float* Sg = state + ((size_t)entry_slot[e] * H + h) * (size_t)D * Dv;
-  float S[Q];
+  float S[CPT][Q];
 #pragma unroll
-  for (int j = 0; j < Q; ++j) {
-    const int i = part * Q + j;
-    S[j] = (col < Dv && !fresh && i < D) ? Sg[(size_t)i * Dv + col] : 0.f;
-  }
+  for (int c = 0; c < CPT; ++c)
+#pragma unroll
+    for (int j = 0; j < Q; ++j) {
+      const int i = part * Q + j;
+      S[c][j] = (col0 + c < Dv && !fresh && i < D) ? Sg[(size_t)i * Dv + col0 + c] : 0.f;
+    }
   auto stage = [&](int chunk, int buf) {
     if (VEC) {
       constexpr int QV = Q / 4, NQK = 2 * PARTS * QV, NV = COLS / 4, ITEMS = NQK + NV;
@@ -170,34 +172,48 @@ __global__ void __launch_bounds__(128) linear_scan_kernel(float* __restrict__ o_
       const float* r = sm + (size_t)((ch & 1) * CH + tk) * ROW;
       const float4* q4 = reinterpret_cast<const float4*>(r + part * SEG);
       const float4* g4 = reinterpret_cast<const float4*>(r + QK + part * SEG);
-      const float v = r[2 * QK + cl];
-      float op[4] = {0.f, 0.f, 0.f, 0.f};
+      float v[CPT], op[CPT][4];
+#pragma unroll
+      for (int c = 0; c < CPT; ++c) {
+        v[c] = r[2 * QK + cl * CPT + c];
+        op[c][0] = op[c][1] = op[c][2] = op[c][3] = 0.f;
+      }
+      // a q / g word read from shared memory serves the thread's CPT columns
 #pragma unroll
       for (int j = 0; j < Q / 4; ++j) {
         const float4 gg = g4[j], qq = q4[j];
-        if (CHANNEL_GATE) {
-          S[4 * j] = v + gg.x * (S[4 * j] - v);
-          S[4 * j + 1] = v + gg.y * (S[4 * j + 1] - v);
-          S[4 * j + 2] = v + gg.z * (S[4 * j + 2] - v);
-          S[4 * j + 3] = v + gg.w * (S[4 * j + 3] - v);
-        } else {
-          S[4 * j] = S[4 * j] * decay + gg.x * v;
-          S[4 * j + 1] = S[4 * j + 1] * decay + gg.y * v;
-          S[4 * j + 2] = S[4 * j + 2] * decay + gg.z * v;
-          S[4 * j + 3] = S[4 * j + 3] * decay + gg.w * v;
+#pragma unroll
+        for (int c = 0; c < CPT; ++c) {
+          float* Sc = S[c];
+          if (CHANNEL_GATE) {
+            Sc[4 * j] = v[c] + gg.x * (Sc[4 * j] - v[c]);
+            Sc[4 * j + 1] = v[c] + gg.y * (Sc[4 * j + 1] - v[c]);
+            Sc[4 * j + 2] = v[c] + gg.z * (Sc[4 * j + 2] - v[c]);
+            Sc[4 * j + 3] = v[c] + gg.w * (Sc[4 * j + 3] - v[c]);
+          } else {
+            Sc[4 * j] = Sc[4 * j] * decay + gg.x * v[c];
+            Sc[4 * j + 1] = Sc[4 * j + 1] * decay + gg.y * v[c];
+            Sc[4 * j + 2] = Sc[4 * j + 2] * decay + gg.z * v[c];
+            Sc[4 * j + 3] = Sc[4 * j + 3] * decay + gg.w * v[c];
+          }
+          op[c][0] += Sc[4 * j] * qq.x; op[c][1] += Sc[4 * j + 1] * qq.y; op[c][2] += Sc[4 * j + 2] * qq.z; op[c][3] += Sc[4 * j + 3] * qq.w;
         }
-        op[0] += S[4 * j] * qq.x; op[1] += S[4 * j + 1] * qq.y; op[2] += S[4 * j + 2] * qq.z; op[3] += S[4 * j + 3] * qq.w;
       }
-      const float o = part_sum<PARTS>((op[0] + op[1]) + (op[2] + op[3]));
-      if (part == 0 && col < Dv) o_raw[(size_t)(s0 + ch * CH + tk) * H * Dv + (size_t)h * Dv + col] = o;
+#pragma unroll
+      for (int c = 0; c < CPT; ++c) {
+        const float o = part_sum<PARTS>((op[c][0] + op[c][1]) + (op[c][2] + op[c][3]));
+        if (part == 0 && col0 + c < Dv) o_raw[(size_t)(s0 + ch * CH + tk) * H * Dv + (size_t)h * Dv + col0 + c] = o;
+      }
     }
     __syncthreads();
   }
 #pragma unroll
-  for (int j = 0; j < Q; ++j) {
-    const int i = part * Q + j;
-    if (col < Dv && i < D) Sg[(size_t)i * Dv + col] = S[j];
-  }
+  for (int c = 0; c < CPT; ++c)
+#pragma unroll
+    for (int j = 0; j < Q; ++j) {
+      const int i = part * Q + j;
+      if (col0 + c < Dv && i < D) Sg[(size_t)i * Dv + col0 + c] = S[c][j];
+    }
 }
 
 // step 3: per (token, head): o * rsqrt(mean(o^2) + eps) [* norm_w] [* silu(gate)]; one warp each.  gate: storage-type rows of `stride`
@@ -224,24 +240,27 @@ __global__ void linear_out_kernel(ST* __restrict__ out, long long out_stride, co
 
 template <bool CHANNEL_GATE>
 int launch_scan(float* o_raw, const float* prep, float* state, const float* head_decay, const int* entry_start, const int* entry_len,
-                const int* entry_slot, const int* entry_pos0, int E, int H, int D, int Dv, cudaStream_t s) {
+                const int* entry_slot, const int* entry_pos0, int T, int E, int H, int D, int Dv, cudaStream_t s) {
   const int P = 2 * H * D + H * Dv;
   const bool vec = D % 4 == 0 && Dv % 4 == 0 && P % 4 == 0 && (reinterpret_cast<uintptr_t>(prep) & 15) == 0;
-#define QS_SCAN(DP, PARTS, CH)                                                                                                                \
+#define QS_SCAN(DP, PARTS, CH, CPT)                                                                                                           \
   do {                                                                                                                                        \
-    constexpr int cols = 128 / PARTS;                                                                                                         \
+    constexpr int cols = 128 / PARTS * CPT;                                                                                                   \
     const size_t smb = (size_t)2 * CH * (2 * PARTS * (DP / PARTS + 4) + cols) * sizeof(float);                                                \
     dim3 grid(E, H, (Dv + cols - 1) / cols);                                                                                                  \
-    auto kern = vec ? linear_scan_kernel<DP, PARTS, CH, CHANNEL_GATE, true> : linear_scan_kernel<DP, PARTS, CH, CHANNEL_GATE, false>;         \
+    auto kern = vec ? linear_scan_kernel<DP, PARTS, CH, CPT, CHANNEL_GATE, true> : linear_scan_kernel<DP, PARTS, CH, CPT, CHANNEL_GATE, false>; \
     if (smb > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smb);                                   \
     kern<<<grid, 128, smb, s>>>(o_raw, prep, state, head_decay, entry_start, entry_len, entry_slot, entry_pos0, H, D, Dv);                    \
   } while (0)
-  // rows of a column per thread: all of them up to 32, 32 above (the parts of a column meet through shuffles)
-  if (D <= 16) QS_SCAN(16, 1, 16);
-  else if (D <= 32) QS_SCAN(32, 1, 16);
-  else if (D <= 64) QS_SCAN(64, 2, 16);
-  else if (D <= 128) QS_SCAN(128, 4, 16);
-  else QS_SCAN(256, 8, 8);
+  // rows of a column per thread: all of them up to 32, 32 or 16 above (the parts of a column meet through shuffles).  Long runs of tokens
+  // (prompt portions) take two adjacent columns per thread where the head has the columns for it: a q / g word read from shared memory then
+  // feeds two columns; steps of mostly single tokens are bound by reading and writing the state and keep one column per thread
+  const bool long_runs = T >= 32 * E;
+  if (D <= 16) QS_SCAN(16, 1, 16, 1);
+  else if (D <= 32) QS_SCAN(32, 1, 16, 1);
+  else if (D <= 64) { if (Dv >= 128 && long_runs) QS_SCAN(64, 2, 16, 2); else QS_SCAN(64, 2, 16, 1); }
+  else if (D <= 128) { if (Dv >= 64 && long_runs) QS_SCAN(128, 8, 16, 2); else QS_SCAN(128, 4, 16, 1); }
+  else QS_SCAN(256, 8, 8, 1);
 #undef QS_SCAN
   return check_cuda(cudaGetLastError(), "hyb linear scan");
 }
@@ -272,7 +291,7 @@ int qs_hyb_gate_recurrence(void* out, int64_t out_stride, float* prep, float* o_
   const int HD = heads * dim, HDv = heads * vdim;
   QS_DT(dtype, (gate_prepare_kernel<__nv_bfloat16><<<tokens_n, 256, 0, s>>>(prep, (const __nv_bfloat16*)proj, stride, f_bias, lower, HD, HDv)),
         (gate_prepare_kernel<float><<<tokens_n, 256, 0, s>>>(prep, (const float*)proj, stride, f_bias, lower, HD, HDv)));
-  if (int rc = launch_scan<true>(o_raw, prep, state, nullptr, entry_start, entry_len, entry_slot, entry_pos0, entries, heads, dim, vdim, s)) return rc;
+  if (int rc = launch_scan<true>(o_raw, prep, state, nullptr, entry_start, entry_len, entry_slot, entry_pos0, tokens_n, entries, heads, dim, vdim, s)) return rc;
   const int warps = tokens_n * heads;
   QS_DT(dtype,
         (linear_out_kernel<__nv_bfloat16><<<(warps + 3) / 4, 128, 0, s>>>((__nv_bfloat16*)out, out_stride, o_raw, norm_w, nullptr, 0, tokens_n, heads,
@@ -296,7 +315,7 @@ int qs_hyb_retention(void* out, int64_t out_stride, float* prep, float* o_raw, c
                                                                            heads, dim, vdim)),
         (retention_prepare_kernel<float><<<tokens_n, 256, rot_dims * sizeof(float), s>>>(prep, (const float*)proj, stride, tok_pos, inv_freq, rot_dims, k_scale, heads, dim,
                                                                   vdim)));
-  if (int rc = launch_scan<false>(o_raw, prep, state, head_decay, entry_start, entry_len, entry_slot, entry_pos0, entries, heads, dim, vdim, s)) return rc;
+  if (int rc = launch_scan<false>(o_raw, prep, state, head_decay, entry_start, entry_len, entry_slot, entry_pos0, tokens_n, entries, heads, dim, vdim, s)) return rc;
   const int warps = tokens_n * heads;
   const size_t gate_off = (size_t)2 * heads * dim + (size_t)heads * vdim;  // the output gate follows q | k | v in the projection row
   QS_DT(dtype,

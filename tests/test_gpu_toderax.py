@@ -101,6 +101,9 @@ def test_router_kernel(dev, experts, top, width):
 LAYERS = [
     gate_layer(mlp=None), gate_layer(heads=1, dim=40, vdim=8, mlp=None), gate_layer(heads=5, dim=4, vdim=72, mlp=None),
     gate_layer(heads=1, dim=128, vdim=32, mlp=None), gate_layer(heads=2, dim=130, vdim=4, mlp=None),
+    gate_layer(heads=2, dim=128, vdim=72, mlp=None), gate_layer(heads=1, dim=64, vdim=136, mlp=None), gate_layer(heads=1, dim=100, vdim=66, mlp=None),
+    pair_layer(heads=2, kv_heads=1, dim=16, vdim=16, chunk=33, r_heads=2, r_dim=128, r_vdim=64, rot_dims=64, mlp=None),
+    pair_layer(heads=2, kv_heads=1, dim=16, vdim=16, chunk=0, r_heads=1, r_dim=64, r_vdim=130, rot_dims=64, mlp=None),
     pair_layer(mlp=None), pair_layer(heads=3, kv_heads=1, dim=20, vdim=12, chunk=0, r_heads=1, r_dim=8, r_vdim=40, rot_dims=8, mlp=None),
     pair_layer(heads=2, kv_heads=2, dim=64, vdim=160, chunk=64, r_heads=2, r_dim=64, r_vdim=16, rot_dims=32, mlp=None),
     pair_layer(heads=1, kv_heads=1, dim=8, vdim=8, chunk=1, r_heads=4, r_dim=24, r_vdim=8, rot_dims=2, mlp=None),
@@ -218,6 +221,16 @@ def test_portions_of_a_prompt(dev, sizes):
     cfg = make_config(MIXED)
     w = make_weights(cfg, 7)
     toks = random_tokens(197, cfg["vocab"], 7)
+    assert row_err(_portions(_engine(cfg, w), "a", toks, sizes), O.forward(cfg, w, toks)) < F32_TOL
+
+
+@pytest.mark.parametrize("sizes", [[1], [40, 1, 2, 70]])
+def test_wide_states_in_long_and_short_runs(dev, sizes):
+    """Head sizes for which long runs of tokens and single tokens take different thread layouts of the recurrence."""
+    cfg = make_config([gate_layer(heads=2, dim=128, vdim=72, mlp=None),
+                       pair_layer(heads=2, kv_heads=1, dim=16, vdim=16, chunk=33, r_heads=1, r_dim=64, r_vdim=130, rot_dims=64, mlp=None)])
+    w = make_weights(cfg, 15)
+    toks = random_tokens(120, cfg["vocab"], 15)
     assert row_err(_portions(_engine(cfg, w), "a", toks, sizes), O.forward(cfg, w, toks)) < F32_TOL
 
 
