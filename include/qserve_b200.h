@@ -263,7 +263,8 @@ QS_API int qs_hyb_gated_delta(void* out, int64_t out_stride, float* prep, float*
                               const int32_t* entry_slot, const int32_t* entry_pos0, int tokens_n, int entries, int heads, int kv_heads,
                               int dim, int vdim, int taps, float unit_eps, float eps, int dtype, void* stream);
 
-/* Residual streams x fp32 [tokens, streams, width] (hyper-connections; streams = 1 with all coefficients 1 is the plain residual).  In order:
+/* Residual streams x fp32 [tokens, streams, width], streams <= 16 (hyper-connections; streams = 1 with all coefficients 1 is the plain
+ * residual).  In order:
  * (upd != NULL) every stream at once from the old ones: x_t <- sum_s upd_mix[s, t] x_s + upd_out[t] upd (upd: [tokens, width], fp32 if
  * upd_f32, else storage type);  u = sum_s in_coef[s] x_s (in_coef NULL: the plain sum);  (out_sum != NULL) out_sum <- u (fp32);
  * (out_h != NULL) out_h <- u brought to unit RMS in `groups` equal consecutive parts, times (offset + w) (storage type; w fp32 [width]). */

@@ -16,7 +16,7 @@ namespace {
 
 using namespace hyb;
 
-constexpr int kMaxStreams = 8;
+constexpr int kMaxStreams = 16;
 
 // ---------------------------------------------------------------------------------------------------------------------------------
 // Residual streams x [tokens][S][W] fp32.  One block per token:
@@ -34,10 +34,10 @@ __global__ void stream_norm_kernel(ST* __restrict__ out_h, float* __restrict__ o
   extern __shared__ float dyn[];  // u [W] | partial sums [groups * per] | 1 / rms [groups]
   __shared__ float c_mix[kMaxStreams * kMaxStreams], c_out[kMaxStreams], c_in[kMaxStreams];
   const int t = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nw = blockDim.x >> 5;
-  if (tid < S * S) c_mix[tid] = upd != nullptr ? mix[tid] : 0.f;
-  if (tid < S) {
-    c_out[tid] = upd != nullptr ? cout[tid] : 0.f;
-    c_in[tid] = cin != nullptr ? cin[tid] : 1.f;
+  for (int i = tid; i < S * S; i += blockDim.x) c_mix[i] = upd != nullptr ? mix[i] : 0.f;
+  for (int i = tid; i < S; i += blockDim.x) {
+    c_out[i] = upd != nullptr ? cout[i] : 0.f;
+    c_in[i] = cin != nullptr ? cin[i] : 1.f;
   }
   __syncthreads();
   float* u_s = dyn;
@@ -108,10 +108,10 @@ __global__ void stream_norm_vec_kernel(ST* __restrict__ out_h, float* __restrict
   extern __shared__ __align__(16) float dyn[];  // u [W] | partial sums [groups * per] | 1 / rms [groups]
   __shared__ float c_mix[S * S], c_out[S], c_in[S];
   const int t = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nw = blockDim.x >> 5;
-  if (tid < S * S) c_mix[tid] = upd != nullptr ? mix[tid] : 0.f;
-  if (tid < S) {
-    c_out[tid] = upd != nullptr ? cout[tid] : 0.f;
-    c_in[tid] = cin != nullptr ? cin[tid] : 1.f;
+  for (int i = tid; i < S * S; i += blockDim.x) c_mix[i] = upd != nullptr ? mix[i] : 0.f;
+  for (int i = tid; i < S; i += blockDim.x) {
+    c_out[i] = upd != nullptr ? cout[i] : 0.f;
+    c_in[i] = cin != nullptr ? cin[i] : 1.f;
   }
   __syncthreads();
   float* u_s = dyn;
@@ -495,7 +495,7 @@ extern "C" {
 int qs_hyb_stream_norm(void* out_h, float* out_sum, float* x, int streams, const void* upd, int upd_f32, const float* upd_mix, const float* upd_out,
                        const float* in_coef, const float* w, int groups, float offset, float eps, int tokens_n, int width, int dtype, void* stream) {
   QS_REQUIRE(x && (out_h == nullptr || w != nullptr), "hyb_stream_norm: null tensor");
-  QS_REQUIRE(streams >= 1 && streams <= kMaxStreams, "hyb_stream_norm: 1..8 streams");
+  QS_REQUIRE(streams >= 1 && streams <= kMaxStreams, "hyb_stream_norm: 1..16 streams");
   QS_REQUIRE(upd == nullptr || (upd_mix && upd_out), "hyb_stream_norm: a pending write needs its coefficients");
   QS_REQUIRE(groups >= 1 && width % groups == 0, "hyb_stream_norm: the width must split into `groups` equal parts");
   if (tokens_n == 0) return qs::QS_OK;
@@ -511,7 +511,7 @@ int qs_hyb_stream_norm(void* out_h, float* out_sum, float* x, int streams, const
                                                          groups, offset, eps, width);                                                  \
   } while (0)
   auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
-  if (width % 4 == 0 && al16(out_h) && al16(out_sum) && al16(x) && al16(upd) && al16(w)) {
+  if (streams <= 8 && width % 4 == 0 && al16(out_h) && al16(out_sum) && al16(x) && al16(upd) && al16(w)) {
 #define QS_VEC(ST, S)                                                                                                                        \
   do {                                                                                                                                       \
     if (smb > 48 * 1024) cudaFuncSetAttribute(stream_norm_vec_kernel<ST, S>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smb);         \

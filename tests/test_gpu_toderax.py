@@ -46,7 +46,7 @@ MIXED = [gate_layer(), pair_layer(), pair_layer(heads=2, kv_heads=2, dim=8, vdim
 # ------------------------------------------------------------------------------------------------------------------------
 # each mechanism alone
 # ------------------------------------------------------------------------------------------------------------------------
-@pytest.mark.parametrize("streams,groups,width", [(0, 1, 48), (1, 1, 40), (3, 2, 48), (4, 6, 36), (8, 5, 35)])
+@pytest.mark.parametrize("streams,groups,width", [(0, 1, 48), (1, 1, 40), (3, 2, 48), (4, 6, 36), (8, 5, 35), (11, 4, 48)])
 def test_embedding_streams_and_group_norm(dev, streams, groups, width):
     """No layers: the scaled embedding in every stream, their sum, the group-wise final norm."""
     cfg = make_config([], streams=streams, groups=groups, width=width, embed_scale=0.5 + streams)
@@ -56,7 +56,7 @@ def test_embedding_streams_and_group_norm(dev, streams, groups, width):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("streams,groups,width", [(1, 1, 40), (3, 2, 48), (8, 5, 35), (2, 1, 2560), (4, 16, 2048)])
+@pytest.mark.parametrize("streams,groups,width", [(1, 1, 40), (3, 2, 48), (8, 5, 35), (2, 1, 2560), (4, 16, 2048), (13, 3, 48), (16, 1, 30)])
 def test_stream_norm_kernel(dev, dtype, streams, groups, width):
     """The streams' kernel alone against its formulas: pending write (fp32 or storage-type rows), read coefficients, sum, group-wise norm."""
     from qserve_b200._lib import check, lib
