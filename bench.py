@@ -769,8 +769,8 @@ def hybrid_block(args):
 # ------------------------------------------------------------------------------------------------------------
 def toderax_block(args):
     """Prefill (4 prompts x 2048 tokens in one step) and decode (64 sequences at 1024 tokens of context) of a four-layer stack
-    gate recurrence | attention + retention | gate recurrence | attention + retention with a mixture of experts (16 experts, 4 per token, plus a
-    shared expert; the experts a token runs hold as many weights as the other model's feed-forward) in every layer, on 4 residual streams.
+    gate recurrence | attention + retention | gate recurrence | attention + retention with a mixture of experts (32 experts, 8 per token, plus a
+    shared expert; the experts a token runs hold as many weights as the other model's feed-forward) in every layer, on 2 residual streams.
     Whole steps are captured in CUDA graphs (device time, host excluded); the design's kernels are timed one by one with their algorithmic
     bytes / flops against the measured copy and bf16 GEMM peaks.  Beside it: the Rizurax stack (attention | delta | attention | delta, dense
     feed-forward) at equal width / heads / head size, and the kernels that play the same parts there."""
@@ -792,7 +792,7 @@ def toderax_block(args):
     stream = torch.cuda.current_stream()
     reps = max(3, args.kernel_reps)
     raw = lambda: torch._C._cuda_getCurrentRawStream(0)
-    B, CTX, NP, LP, NS, E, TOP = 64, 1024, 4, 2048, 4, 16, 4
+    B, CTX, NP, LP, NS, NG, E, TOP = 64, 1024, 4, 2048, 2, 8, 32, 8
     out = {"metric": "Toderax decoder throughput (tokens/s, random weights, bf16, 4 layers)", "unit": "tokens/s", "impl": "ours", "dtype": "bf16",
            "data": "synthetic", "peaks": {"hbm_gbs": hbm_gbs, "bf16_tflops": tflops}, "sizes": {}}
 
@@ -830,7 +830,7 @@ def toderax_block(args):
         moe = MoeConfig(E, TOP, FF // TOP, 7.0, FF // TOP, 7.0)
         cfg = HybridConfig("Toderax", V, W, 1e-5, tuple(HybridLayerConfig(t, m, moe) for t, m in
                                                        (("hgrn2", gate), ("parallel", par), ("hgrn2", gate), ("parallel", par))),
-                           norm_offset=0.0, block="sequential", streams=NS, norm_groups=4, embed_scale=4.0)
+                           norm_offset=0.0, block="sequential", streams=NS, norm_groups=NG, embed_scale=4.0)
         g = torch.Generator().manual_seed(0)
         rec = {}
         with torch.no_grad():
@@ -849,14 +849,14 @@ def toderax_block(args):
             tp, td = mixer_times(ly_p.mixer.right, eng.cache.runs[1]["right"], pb, db, T)
             kern["retention_prefill(rotate+scan+gate)"] = {"us": tp * 1e6, "tokens_per_s": T / tp, "heads": H // 2}
             kern["retention_decode(rotate+scan+gate)"] = {"us": td * 1e6, "frac_of_measured_hbm": B * (H // 2) * D * D * 8 / td / 1e9 / hbm_gbs}
-            # the streams' kernel as the engine runs it: a pending bf16 write lands in 4 fp32 streams, one normalised bf16 row leaves
+            # the streams' kernel as the engine runs it: a pending bf16 write lands in the fp32 streams, one normalised bf16 row leaves
             x = torch.randn(T, NS, W, device=dev)
             h1, upd = torch.empty(T, W, dtype=torch.bfloat16, device=dev), torch.zeros(T, W, dtype=torch.bfloat16, device=dev)
             hc = ly_g.hc2
             tn = time_kernel(lambda: (check(lib.qs_hyb_stream_norm(h1.data_ptr(), None, x.data_ptr(), NS, upd.data_ptr(), 0, hc.mix.data_ptr(),
-                                                                   hc.cout.data_ptr(), hc.cin.data_ptr(), ly_g.norm2.data_ptr(), 4, 0.0, 1e-5, T, W, 0,
+                                                                   hc.cout.data_ptr(), hc.cin.data_ptr(), ly_g.norm2.data_ptr(), NG, 0.0, 1e-5, T, W, 0,
                                                                    raw())), 1)[1], reps, stream)
-            kern["stream_write_read_group_norm(4 streams)"] = {"us": tn * 1e6, "frac_of_measured_hbm": T * W * (NS * 8 + 4) / tn / 1e9 / hbm_gbs}
+            kern[f"stream_write_read_group_norm({NS} streams)"] = {"us": tn * 1e6, "frac_of_measured_hbm": T * W * (NS * 8 + 4) / tn / 1e9 / hbm_gbs}
             ya, yb, y32 = torch.randn(T, W, device=dev).bfloat16(), torch.randn(T, W, device=dev).bfloat16(), torch.empty(T, W, device=dev)
             tb = time_kernel(lambda: (check(lib.qs_hyb_branch_norm_mean(y32.data_ptr(), ya.data_ptr(), yb.data_ptr(), ly_p.mixer.gain_left.data_ptr(),
                                                                         ly_p.mixer.gain_right.data_ptr(), 0.5, 1e-5, T, W, 0, raw())), 1)[1], reps, stream)

@@ -286,54 +286,85 @@ __global__ void qk_prepare_append_kernel(ST* __restrict__ proj, long long stride
 // lower index) as they are (no renormalisation).  One block per token; a warp per expert for the dot products.
 //   route [tokens][E] fp32: the score of a chosen expert, 0 elsewhere;   top_idx / top_w [tokens][top]: the chosen experts, best first
 // ---------------------------------------------------------------------------------------------------------------------------------
-template <typename ST>
-__global__ void moe_router_kernel(float* __restrict__ route, int* __restrict__ top_idx, float* __restrict__ top_w, const ST* __restrict__ h,
-                                  const float* __restrict__ w_router, int W, int E, int top) {
-  extern __shared__ float dyn[];  // h [W] | scores [E]
-  float* hs = dyn;
-  float* z = dyn + W;
-  const int t = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nw = blockDim.x >> 5;
-  for (int i = tid; i < W; i += blockDim.x) hs[i] = ldf(h + (size_t)t * W + i);
+constexpr int kRouterEPW = 4;
+
+template <typename ST, int TOK>
+__global__ void __launch_bounds__(256) moe_router_kernel(float* __restrict__ route, int* __restrict__ top_idx, float* __restrict__ top_w,
+                                                         const ST* __restrict__ h, const float* __restrict__ w_router, int T, int W, int E, int top) {
+  // TOK tokens per block (rows h [TOK][W] in shared memory, storage type) and kRouterEPW experts per warp: a router word read from global
+  // memory meets TOK rows, a row word read from shared memory meets kRouterEPW experts.  The dot product of a (token, expert) pair is summed
+  // in the same order (lane-strided partial sums, then a shuffle tree) whatever else the block holds.  Scores [TOK][E] follow the rows.
+  extern __shared__ __align__(16) unsigned char dyn_raw[];
+  ST* hs = reinterpret_cast<ST*>(dyn_raw);
+  float* z = reinterpret_cast<float*>(dyn_raw + (((size_t)TOK * W * sizeof(ST) + 15) & ~(size_t)15));
+  const int t0 = blockIdx.x * TOK, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nw = blockDim.x >> 5;
+  const int nt = min(TOK, T - t0);
+  for (int i = tid; i < nt * W; i += blockDim.x) hs[i] = h[(size_t)t0 * W + i];
+  for (int i = nt * W + tid; i < TOK * W; i += blockDim.x) stf(hs + i, 0.f);
   __syncthreads();
-  for (int e = warp; e < E; e += nw) {
-    const float* wr = w_router + (size_t)e * W;
-    float d = 0.f;
-    for (int i = lane; i < W; i += 32) d += hs[i] * wr[i];
-    d = warp_sum(d);
-    if (lane == 0) z[e] = d;
-  }
-  __syncthreads();
-  if (warp != 0) return;
-  float mx = -INFINITY;
-  for (int e = lane; e < E; e += 32) mx = fmaxf(mx, z[e]);
-  mx = warp_max(mx);
-  float sum = 0.f;
-  for (int e = lane; e < E; e += 32) sum += expf(z[e] - mx);
-  sum = warp_sum(sum);
-  const float inv = 1.f / sum;
-  for (int e = lane; e < E; e += 32) {
-    z[e] = expf(z[e] - mx) * inv;
-    route[(size_t)t * E + e] = 0.f;
-  }
-  __syncwarp();
-  for (int k = 0; k < top; ++k) {
-    float best = -1.f;
-    int bi = E;
-    for (int e = lane; e < E; e += 32)
-      if (z[e] > best) { best = z[e]; bi = e; }  // strict: the lowest index of a lane's equal scores stays
+  for (int e0 = warp * kRouterEPW; e0 < E; e0 += nw * kRouterEPW) {
+    const float* wr[kRouterEPW];
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
-      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-      if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
+    for (int j = 0; j < kRouterEPW; ++j) wr[j] = w_router + (size_t)min(e0 + j, E - 1) * W;  // experts past the last repeat it and are dropped
+    float d[kRouterEPW][TOK];
+#pragma unroll
+    for (int j = 0; j < kRouterEPW; ++j)
+#pragma unroll
+      for (int k = 0; k < TOK; ++k) d[j][k] = 0.f;
+    for (int i = lane; i < W; i += 32) {
+      float hv[TOK];
+#pragma unroll
+      for (int k = 0; k < TOK; ++k) hv[k] = ldf(hs + k * W + i);
+#pragma unroll
+      for (int j = 0; j < kRouterEPW; ++j) {
+        const float wv = wr[j][i];
+#pragma unroll
+        for (int k = 0; k < TOK; ++k) d[j][k] += hv[k] * wv;
+      }
     }
-    if (lane == 0) {
-      route[(size_t)t * E + bi] = best;
-      top_idx[(size_t)t * top + k] = bi;
-      top_w[(size_t)t * top + k] = best;
-      z[bi] = -1.f;  // scores are positive: taken
+#pragma unroll
+    for (int j = 0; j < kRouterEPW; ++j)
+#pragma unroll
+      for (int k = 0; k < TOK; ++k) {
+        const float v = warp_sum(d[j][k]);
+        if (lane == 0 && e0 + j < E) z[k * E + e0 + j] = v;
+      }
+  }
+  __syncthreads();
+  for (int k = warp; k < nt; k += nw) {  // a warp finishes a token: softmax over all experts, then the `top` largest one by one
+    const size_t t = t0 + k;
+    float* zk = z + k * E;
+    float mx = -INFINITY;
+    for (int e = lane; e < E; e += 32) mx = fmaxf(mx, zk[e]);
+    mx = warp_max(mx);
+    float sum = 0.f;
+    for (int e = lane; e < E; e += 32) sum += expf(zk[e] - mx);
+    sum = warp_sum(sum);
+    const float inv = 1.f / sum;
+    for (int e = lane; e < E; e += 32) {
+      zk[e] = expf(zk[e] - mx) * inv;
+      route[t * E + e] = 0.f;
     }
     __syncwarp();
+    for (int j = 0; j < top; ++j) {
+      float best = -1.f;
+      int bi = E;
+      for (int e = lane; e < E; e += 32)
+        if (zk[e] > best) { best = zk[e]; bi = e; }  // strict: the lowest index of a lane's equal scores stays
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
+      }
+      if (lane == 0) {
+        route[t * E + bi] = best;
+        top_idx[t * top + j] = bi;
+        top_w[t * top + j] = best;
+        zk[bi] = -1.f;  // scores are positive: taken
+      }
+      __syncwarp();
+    }
   }
 }
 
@@ -586,14 +617,28 @@ int qs_hyb_moe_router(float* route, int32_t* top_idx, float* top_w, const void* 
   QS_REQUIRE(experts >= 1 && top >= 1 && top <= experts, "hyb_moe_router: 1 <= top <= experts");
   if (tokens_n == 0) return qs::QS_OK;
   cudaStream_t s = (cudaStream_t)stream;
-  const size_t smb = ((size_t)width + experts) * sizeof(float);
+  // tokens per block: as many as fit beside their scores in shared memory, at most 8; few tokens (decoding) go one per block
+  const size_t es = dtype == QS_DTYPE_BF16 ? 2 : 4;
+  auto bytes = [&](int tk) { return (((size_t)tk * width * es + 15) & ~(size_t)15) + (size_t)tk * experts * sizeof(float); };
+  int tok = tokens_n >= 512 ? 8 : 1;  // every block reads the whole router once (16 tokens per block ran slower: 64 + 16 live accumulators)
+  while (tok > 1 && bytes(tok) > 100 * 1024) tok >>= 1;  // two blocks per SM
+  const size_t smb = bytes(tok);
   QS_REQUIRE(smb <= 200 * 1024, "hyb_moe_router: row too wide for shared memory");
-#define QS_LAUNCH(ST)                                                                                                              \
-  do {                                                                                                                             \
-    if (smb > 48 * 1024) cudaFuncSetAttribute(moe_router_kernel<ST>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smb);       \
-    moe_router_kernel<ST><<<tokens_n, 256, smb, s>>>(route, top_idx, top_w, (const ST*)h, w_router, width, experts, top);          \
+#define QS_LAUNCH(ST, TOK)                                                                                                              \
+  do {                                                                                                                                  \
+    if (smb > 48 * 1024) cudaFuncSetAttribute(moe_router_kernel<ST, TOK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smb);       \
+    moe_router_kernel<ST, TOK><<<(tokens_n + TOK - 1) / TOK, 256, smb, s>>>(route, top_idx, top_w, (const ST*)h, w_router, tokens_n,   \
+                                                                          width, experts, top);                                        \
   } while (0)
-  QS_DT(dtype, QS_LAUNCH(__nv_bfloat16), QS_LAUNCH(float));
+#define QS_LAUNCH_T(ST)                          \
+  switch (tok) {                                 \
+    case 8: QS_LAUNCH(ST, 8); break;             \
+    case 4: QS_LAUNCH(ST, 4); break;             \
+    case 2: QS_LAUNCH(ST, 2); break;             \
+    default: QS_LAUNCH(ST, 1); break;            \
+  }
+  QS_DT(dtype, QS_LAUNCH_T(__nv_bfloat16), QS_LAUNCH_T(float));
+#undef QS_LAUNCH_T
 #undef QS_LAUNCH
   return check_cuda(cudaGetLastError(), "hyb_moe_router");
 }

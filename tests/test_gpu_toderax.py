@@ -80,12 +80,13 @@ def test_stream_norm_kernel(dev, dtype, streams, groups, width):
         assert row_err(h, O.group_norm(u, 0.25 + gain, groups, 1e-5)) < (1e-5 if dtype == torch.float32 else 2.0 ** -8)
 
 
-@pytest.mark.parametrize("experts,top,width", [(6, 2, 48), (1, 1, 16), (40, 40, 33), (64, 7, 2048), (5, 4, 8)])
-def test_router_kernel(dev, experts, top, width):
+@pytest.mark.parametrize("T", [9, 1029, 2050])
+@pytest.mark.parametrize("experts,top,width", [(6, 2, 48), (1, 1, 16), (40, 40, 33), (64, 7, 2048), (5, 4, 8), (3, 2, 8200)])
+def test_router_kernel(dev, experts, top, width, T):
+    """One token per block (few tokens) and several tokens per block sharing the router rows (many tokens)."""
     from qserve_b200._lib import check, lib
 
     g = torch.Generator().manual_seed(experts)
-    T = 9
     h, wr = torch.randn(T, width, generator=g), torch.randn(experts, width, generator=g) * width ** -0.5
     hd, wd = h.to(dev), wr.to(dev)
     route, idx, wt = torch.zeros(T, experts, device=dev), torch.zeros(T, top, dtype=torch.int32, device=dev), torch.zeros(T, top, device=dev)
