@@ -260,7 +260,8 @@ int launch_scan(float* o_raw, const float* prep, float* state, const float* head
   else if (D <= 32) QS_SCAN(32, 1, 16, 1);
   else if (D <= 64) { if (Dv >= 128 && long_runs) QS_SCAN(64, 2, 16, 2); else QS_SCAN(64, 2, 16, 1); }
   else if (D <= 128) { if (Dv >= 64 && long_runs) QS_SCAN(128, 8, 16, 2); else QS_SCAN(128, 4, 16, 1); }
-  else QS_SCAN(256, 8, 8, 1);
+  else if (D <= 256) QS_SCAN(256, 8, 8, 1);
+  else QS_SCAN(512, 16, 4, 1);
 #undef QS_SCAN
   return check_cuda(cudaGetLastError(), "hyb linear scan");
 }
@@ -285,7 +286,7 @@ int qs_hyb_gate_recurrence(void* out, int64_t out_stride, float* prep, float* o_
                            float eps, int dtype, void* stream) {
   QS_REQUIRE(out && prep && o_raw && proj && f_bias && lower && state, "hyb_gate_recurrence: null tensor");
   QS_REQUIRE(entry_start && entry_len && entry_slot && entry_pos0, "hyb_gate_recurrence: null batch table");
-  QS_REQUIRE(heads > 0 && dim > 0 && dim <= 256 && vdim > 0, "hyb_gate_recurrence: 0 < dim <= 256");
+  QS_REQUIRE(heads > 0 && dim > 0 && dim <= 512 && vdim > 0, "hyb_gate_recurrence: 0 < dim <= 512");
   if (tokens_n == 0) return qs::QS_OK;
   cudaStream_t s = (cudaStream_t)stream;
   const int HD = heads * dim, HDv = heads * vdim;
@@ -306,7 +307,7 @@ int qs_hyb_retention(void* out, int64_t out_stride, float* prep, float* o_raw, c
                      int entries, int heads, int dim, int vdim, float eps, int dtype, void* stream) {
   QS_REQUIRE(out && prep && o_raw && proj && head_decay && state && tok_pos, "hyb_retention: null tensor");
   QS_REQUIRE(entry_start && entry_len && entry_slot && entry_pos0, "hyb_retention: null batch table");
-  QS_REQUIRE(heads > 0 && dim > 0 && dim <= 256 && vdim > 0, "hyb_retention: 0 < dim <= 256");
+  QS_REQUIRE(heads > 0 && dim > 0 && dim <= 512 && vdim > 0, "hyb_retention: 0 < dim <= 512");
   QS_REQUIRE(rot_dims >= 0 && rot_dims % 2 == 0 && rot_dims <= dim && (rot_dims == 0 || inv_freq != nullptr), "hyb_retention: bad rotary size");
   if (tokens_n == 0) return qs::QS_OK;
   cudaStream_t s = (cudaStream_t)stream;

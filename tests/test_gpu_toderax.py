@@ -103,6 +103,8 @@ LAYERS = [
     gate_layer(mlp=None), gate_layer(heads=1, dim=40, vdim=8, mlp=None), gate_layer(heads=5, dim=4, vdim=72, mlp=None),
     gate_layer(heads=1, dim=128, vdim=32, mlp=None), gate_layer(heads=2, dim=130, vdim=4, mlp=None),
     gate_layer(heads=2, dim=128, vdim=72, mlp=None), gate_layer(heads=1, dim=64, vdim=136, mlp=None), gate_layer(heads=1, dim=100, vdim=66, mlp=None),
+    gate_layer(heads=1, dim=300, vdim=12, mlp=None), gate_layer(heads=1, dim=512, vdim=8, mlp=None),
+    pair_layer(heads=2, kv_heads=1, dim=16, vdim=16, chunk=20, r_heads=1, r_dim=260, r_vdim=12, rot_dims=64, mlp=None),
     pair_layer(heads=2, kv_heads=1, dim=16, vdim=16, chunk=33, r_heads=2, r_dim=128, r_vdim=64, rot_dims=64, mlp=None),
     pair_layer(heads=2, kv_heads=1, dim=16, vdim=16, chunk=0, r_heads=1, r_dim=64, r_vdim=130, rot_dims=64, mlp=None),
     pair_layer(mlp=None), pair_layer(heads=3, kv_heads=1, dim=20, vdim=12, chunk=0, r_heads=1, r_dim=8, r_vdim=40, rot_dims=8, mlp=None),
