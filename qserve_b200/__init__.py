@@ -6,7 +6,8 @@ the reference's module names.  Importing `qserve_b200.backend` (or `qserve_backe
 fails loudly if it has not been built (`python -m qserve_b200.build`); there is no CPU fallback.
 
 Unquantised hybrid decoders (attention layers beside recurrent layers, fp32 residual stream) are served by `qserve_b200.engine.Engine`:
-`modelcfg` (config.json parsers by architecture name), `hybrid` (model and mixers over csrc/hybrid.cu), `cache` (page pool and state slots),
+`modelcfg` (config.json parsers by architecture name: Rizurax, Toderax), `hybrid` (model, mixers and feed-forwards over csrc/hybrid*.cu),
+`cache` (page pool and state slots),
 `engine` (scheduler, step function, sampling, trace replay), `cli` (`python -m qserve_b200.cli generate|trace`, `bin/trace_run`).
 """
 __all__ = ["backend", "build", "cache", "cli", "decode", "engine", "hybrid", "modelcfg", "tp"]

@@ -3,7 +3,8 @@ state slots (one per live sequence) for what a recurrent layer carries from toke
 
 * Pages hold `page_size` positions.  A sequence owns a list of pages (its block-table row); page ids are valid in every attention layer
   run's K and V pool, as in the reference's block manager (qserve/core/block_manager.py: one block table per sequence, all layers).
-* A slot holds, per recurrent layer run, the fp32 state and the convolution's last inputs; the slot index is also the block-table row.
+* A slot holds, per recurrent layer run, the fp32 state (and, for the delta rule, the convolution's last inputs); the slot index is also the
+  block-table row.  Two mixers side by side keep their storage side by side ("left" / "right").
 * Released pages and slots go back to LIFO free lists and are handed out again first: nothing is cleared on release, a recurrent layer
   starts a sequence (position 0) from zero by itself and attention never reads beyond a sequence's own length.
 """
